@@ -1,0 +1,220 @@
+/*
+ * arcb200 — C ABI of the B200 (sm_100a) inference path for the mdlARC_scale
+ * TinyTransformer: packed-prompt prefill, static-KV-cache greedy decode
+ * (one CUDA graph per decode step) and the standalone kernels behind them.
+ *
+ * The reference project is pure Python and has no FFI of its own; each entry
+ * point below therefore cites the reference *Python* function whose device
+ * work it replaces (paths are relative to the reference repository root).
+ *
+ * Conventions
+ *   - every pointer named d_* is a DEVICE pointer owned by the caller
+ *     (normally a torch tensor); the library borrows it for the call, or for
+ *     the life of the session when it is part of arcb_session_desc;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - return value: 0 = ok, <0 = argument/state error (ARCB_E_*), >0 = a
+ *     cudaError_t / CUresult value; arcb_last_error() gives a message;
+ *   - no exceptions cross the boundary, no global state besides the handles
+ *     (except the statically allocated scratch of the *_static entry point,
+ *     documented there).
+ */
+#ifndef ARCB200_H
+#define ARCB200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ARCB_OK 0
+#define ARCB_E_ARG (-1)       /* bad argument / unsupported shape            */
+#define ARCB_E_STATE (-2)     /* call order (weights missing, no prefill...)  */
+#define ARCB_E_DEVICE (-3)    /* a kernel reported a device-side error word   */
+#define ARCB_E_UNSUPPORTED (-4)
+
+#define ARCB_ACT_F16 0  /* 16-bit activations held as IEEE half (default)     */
+#define ARCB_ACT_BF16 1 /* 16-bit activations held as bfloat16                */
+
+#define ARCB_GEMM_AUTO 0 /* tcgen05 GEMM when M > 32, weight-streaming below   */
+#define ARCB_GEMM_SIMT 1 /* CUDA-core GEMM everywhere (debug cross-check)      */
+#define ARCB_GEMM_TC 2   /* tcgen05 GEMM everywhere                            */
+
+#define ARCB_ATTN_AUTO 0   /* tcgen05 flash prefill when available             */
+#define ARCB_ATTN_STREAM 1 /* per-query streaming kernel for prefill as well   */
+
+typedef struct arcb_engine arcb_engine;
+typedef struct arcb_session arcb_session;
+
+/* Mirrors TransformerConfig (src/transformer.py:15-34). Only rope_type "3d",
+ * norm_type "rmsnorm", ffn_type "swiglu", vocab_size 14 and head_dim 64 are
+ * implemented; anything else is rejected by the host wrapper. */
+typedef struct arcb_config {
+  int32_t d_model;
+  int32_t n_heads;
+  int32_t n_layers;
+  int32_t d_ff;
+  int32_t vocab_size;
+  int32_t num_examples;
+  int32_t max_x, max_y, max_z; /* RoPE table extents (positions clamp to max-1) */
+  int32_t use_example_embedding;
+  int32_t act_format; /* ARCB_ACT_*  */
+  int32_t gemm_path;  /* ARCB_GEMM_* */
+  int32_t attn_path;  /* ARCB_ATTN_* */
+  float norm_eps;
+} arcb_config;
+
+/* Tensor kinds for arcb_engine_load_tensor: names follow the reference
+ * state_dict (src/transformer.py:523-542, 245-263, 436-443). All sources are
+ * fp32, row-major, in the reference's own shapes. */
+enum arcb_tensor_kind {
+  ARCB_T_TOKEN_EMBED = 0, /* token_embed.weight           [vocab, d]        */
+  ARCB_T_EXAMPLE_EMBED,   /* example_embed.weight         [num_examples, d] */
+  ARCB_T_LN1_W,           /* blocks.L.ln1.weight          [d]               */
+  ARCB_T_QKV_W,           /* blocks.L.attn.qkv_proj.weight [3d, d]          */
+  ARCB_T_OUT_W,           /* blocks.L.attn.out_proj.weight [d, d]           */
+  ARCB_T_LN2_W,           /* blocks.L.ln2.weight          [d]               */
+  ARCB_T_GATE_W,          /* blocks.L.ffn.fc_gate.weight  [dff, d]          */
+  ARCB_T_GATE_B,          /* blocks.L.ffn.fc_gate.bias    [dff]             */
+  ARCB_T_UP_W,            /* blocks.L.ffn.fc_up.weight    [dff, d]          */
+  ARCB_T_UP_B,            /* blocks.L.ffn.fc_up.bias      [dff]             */
+  ARCB_T_DOWN_W,          /* blocks.L.ffn.fc_down.weight  [d, dff]          */
+  ARCB_T_DOWN_B,          /* blocks.L.ffn.fc_down.bias    [d]               */
+  ARCB_T_LNF_W,           /* ln_f.weight                  [d]               */
+  ARCB_T_LM_HEAD,         /* lm_head.weight               [vocab, d]        */
+  ARCB_T_ROPE_COS_X,      /* blocks.0.attn.rope.cos_x     [max_x, 10]       */
+  ARCB_T_ROPE_SIN_X,
+  ARCB_T_ROPE_COS_Y,      /*                              [max_y, 10]       */
+  ARCB_T_ROPE_SIN_Y,
+  ARCB_T_ROPE_COS_Z,      /*                              [max_z, 12]       */
+  ARCB_T_ROPE_SIN_Z,
+  ARCB_T_COUNT
+};
+
+const char* arcb_last_error(void);
+/* 1 when the library was compiled for sm_100a and a device of compute
+ * capability 10.x is current, else 0. */
+int arcb_device_ok(void);
+
+/* ---- engine: packed weights of one model ------------------------------ */
+
+/* Replaces moving a TinyTransformer to the device (src/eval.py:881-951 ends in
+ * model.to(device)); the engine keeps its own bf16 copies in kernel layout. */
+int arcb_engine_create(const arcb_config* cfg, arcb_engine** out);
+int arcb_engine_destroy(arcb_engine* eng);
+
+/* Round one fp32 tensor to bf16 and store it in kernel layout.  `layer` is
+ * ignored for the model-level kinds.  The copy/convert runs on `stream`. */
+int arcb_engine_load_tensor(arcb_engine* eng, int32_t kind, int32_t layer, const float* d_src,
+                            int64_t numel, void* stream);
+
+/* ---- session: one batch of sequences sharing a static KV cache --------- */
+
+/* StaticKVCache + GridStateUpdater + the per-call tensors of generate_output
+ * (src/inference.py:51-96, 104-168, 539-558). */
+typedef struct arcb_session_desc {
+  int32_t n_seqs;             /* B: cache rows                                        */
+  int32_t t_max;              /* cache positions per sequence                         */
+  int32_t max_new;            /* generated-token budget per sequence                  */
+  int32_t max_prefill_tokens; /* largest packed-token count of one arcb_prefill call  */
+  int32_t attn_splits;        /* split-K factor of decode attention; 0 = choose       */
+  int32_t stop_on_end;        /* 1: a row that emits END is frozen (emits END after)  */
+  void* d_kv_cache;           /* bf16 [L][2][B][H][t_max][64]                         */
+  int64_t kv_cache_bytes;
+  void* d_workspace;          /* >= arcb_session_workspace_bytes(...)                 */
+  int64_t workspace_bytes;
+  int32_t* d_out_tokens;      /* int32 [B][max_new]: generated tokens                 */
+  const int32_t* d_forced;    /* optional int32 [B][max_new]: teacher-forced tokens   */
+  float* d_step_logits;       /* optional fp32 [B][max_new][14]: logits of every step */
+} arcb_session_desc;
+
+int64_t arcb_session_workspace_bytes(const arcb_engine* eng, int32_t n_seqs,
+                                     int32_t max_prefill_tokens, int32_t attn_splits);
+int64_t arcb_kv_cache_bytes(const arcb_engine* eng, int32_t n_seqs, int32_t t_max);
+int arcb_session_create(arcb_engine* eng, const arcb_session_desc* desc, arcb_session** out);
+int arcb_session_destroy(arcb_session* s);
+
+/* One packed-prompt forward over the cache: _prefill (src/inference.py:383-424)
+ * and, with d_logits_all, TinyTransformer.forward (src/transformer.py:562-599).
+ *
+ * Rows are query tokens in any order grouped by sequence.  A row with
+ * kv_slot >= 0 stores its K/V at that cache position of its sequence; a row
+ * with kv_slot < 0 is query-only (a padded position).  kv_count is the number
+ * of cached positions [0, kv_count) the row attends to (causal AND key-padding
+ * mask expressed as a prefix length over the compacted keys).
+ *
+ * The n_first rows named by d_first_row produce the first generated token of
+ * the sequences d_first_seq (src/inference.py:417-424, 573-590) and arm the
+ * decode state of those sequences (prompt length, grid state, example id). */
+typedef struct arcb_prefill_args {
+  int32_t n_tokens;
+  const int32_t* d_token_ids;  /* [n_tokens]                                   */
+  const int32_t* d_pos_xyz;    /* [n_tokens][3]                                */
+  const int32_t* d_seq;        /* [n_tokens] cache row of each token           */
+  const int32_t* d_kv_slot;    /* [n_tokens]                                   */
+  const int32_t* d_kv_count;   /* [n_tokens]                                   */
+  const int32_t* d_example_ids; /* [B] indexed by cache row (NULL = no example embedding) */
+  /* flash-prefill work list: query blocks of <=128 consecutive rows of one sequence */
+  int32_t n_qblocks;
+  const int32_t* d_qblock_row0; /* [n_qblocks] first packed row                */
+  const int32_t* d_qblock_rows; /* [n_qblocks] rows in block (1..128)          */
+  float* d_logits_all;         /* optional [n_tokens][14]                      */
+  int32_t n_first;
+  const int32_t* d_first_row;  /* [n_first] packed row whose hidden state is read */
+  const int32_t* d_first_seq;  /* [n_first] cache row it belongs to            */
+  const int32_t* d_prompt_len; /* [n_first] cached prompt positions of that row   */
+  const int32_t* d_grid_x;     /* [n_first] _derive_initial_state_from_prompt  */
+  const int32_t* d_grid_y;     /*           (src/inference.py:171-221)         */
+  const int32_t* d_grid_in_output;
+  float* d_first_logits;       /* optional [n_first][14]                       */
+} arcb_prefill_args;
+
+int arcb_prefill(arcb_session* s, const arcb_prefill_args* a, void* stream);
+
+/* n_steps iterations of the greedy loop body (src/inference.py:593-626):
+ * GridStateUpdater.update -> _decode_step -> argmax -> finished/END handling,
+ * each iteration one replay of a CUDA graph captured on first use. */
+int arcb_decode(arcb_session* s, int32_t n_steps, void* stream);
+
+/* Synchronises `stream`, then reports how many rows have emitted END and the
+ * device error word (0 = none). Replaces `finished.all()` (src/inference.py:594). */
+int arcb_session_poll(arcb_session* s, int32_t* n_finished, int32_t* device_error, void* stream);
+
+/* Number of kernels the library has launched since the counter was last reset
+ * (graph replays count the kernels inside the graph). */
+int64_t arcb_launch_count(int reset);
+
+/* ---- standalone operators (unit tests, profiling, partial adoption) ---- */
+
+/* RMSNorm.forward (src/transformer.py:45-48): out16 = act(x*rsqrt(mean(x^2)+eps)*w) */
+int arcb_op_rmsnorm(const float* d_x, const float* d_w, void* d_out16, int32_t rows, int32_t d,
+                    float eps, int32_t act_format, void* stream);
+
+/* y[M,N] (fp32) = A[M,K] (16-bit, act_format) * W[N,K]^T (bf16): nn.Linear without
+ * bias as used at src/inference.py:402,410 / src/transformer.py:260-263.
+ * gemm_path selects the tcgen05 or the CUDA-core kernel. */
+int arcb_op_gemm(const void* d_a16, const void* d_w_bf16, float* d_y, int32_t M, int32_t N,
+                 int32_t K, int32_t act_format, int32_t gemm_path, void* stream);
+
+/* Attention of one query vector per item over a cached K/V prefix:
+ * F.scaled_dot_product_attention at src/inference.py:452 (is_causal=False, key mask
+ * expressed as a length).  q16/out16: [n_items][H][64]; K, V: [B][H][t_max][64] bf16;
+ * item i reads cache row d_item_seq[i] (NULL = i), positions [0, d_item_len[i]).
+ * With n_splits > 1, d_scratch must hold arcb_attn_scratch_bytes(...) bytes. */
+int64_t arcb_attn_scratch_bytes(int32_t n_items, int32_t n_heads, int32_t n_splits);
+int arcb_op_decode_attention(const void* d_q16, const void* d_k, const void* d_v, void* d_out16,
+                             const int32_t* d_item_seq, const int32_t* d_item_len,
+                             const uint8_t* d_item_skip, int32_t n_items, int32_t n_heads,
+                             int32_t t_max, int32_t n_splits, void* d_scratch, int32_t act_format,
+                             void* stream);
+
+/* ln_f -> lm_head -> argmax (src/inference.py:418/424/459 + 574/611): logits fp32
+ * [rows][14] and the index of the first maximum. d_row_index (optional) gathers rows of x. */
+int arcb_op_head(const float* d_x, const int32_t* d_row_index, const float* d_lnf_w,
+                 const float* d_lm_head, float* d_logits, int32_t* d_argmax, int32_t rows,
+                 int32_t d, float eps, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ARCB200_H */

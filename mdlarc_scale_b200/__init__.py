@@ -1,0 +1,23 @@
+"""B200-native greedy generation + AAIVR voting for the mdlARC_scale TinyTransformer.
+
+Public API (same call signatures as the reference's ``src/inference.py`` / ``src/voting.py``):
+``generate_output``, ``predict_with_augmentations``, ``forward_logits``, ``aaivr_predict``,
+``aggregate_votes``, ``compute_voting_stats``.
+"""
+from .voting import aaivr_predict, aggregate_votes, compute_voting_stats, select_top_k  # noqa: F401
+
+__all__ = ["generate_output", "predict_with_augmentations", "forward_logits", "aaivr_predict",
+           "aggregate_votes", "compute_voting_stats", "select_top_k", "Engine"]
+
+
+def __getattr__(name):  # torch-dependent parts are imported lazily
+    if name in ("generate_output", "predict_with_augmentations", "generate_tokens"):
+        from . import inference
+        return getattr(inference, name)
+    if name in ("forward_logits", "B200TinyTransformer"):
+        from . import transformer
+        return getattr(transformer, name)
+    if name in ("Engine", "engine_for"):
+        from . import engine
+        return getattr(engine, name)
+    raise AttributeError(name)

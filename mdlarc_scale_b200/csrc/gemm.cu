@@ -1,0 +1,365 @@
+// y = A[M,K] (16-bit activations) * W[N,K]^T (bf16 weights), fp32 accumulate, with the
+// fused epilogues of epilogue.cuh.  Two kernels:
+//   gemm_tc_kernel   : tcgen05.mma (UMMA 128xBNx16, accumulator in TMEM), operands
+//                      staged by TMA (128-byte swizzle) through an mbarrier ring;
+//                      warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.
+//   gemm_simt_kernel : CUDA-core tile kernel for skinny M (weight streaming) and as
+//                      the cross-check of the tensor-core path.
+#include "gemm.cuh"
+#include "ptx_sm100.cuh"
+
+using namespace sm100;
+
+// ---------------------------------------------------------------------------
+// tcgen05 kernel
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;  // 64 x 2 B = one 128-byte swizzle row
+
+template <int BN>
+struct TcCfg {
+  static constexpr int STAGES = (BN == 128) ? 3 : 4;
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  // stages + barriers (full, empty per stage, acc) + tmem slot, + 1024 alignment slack
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int BN, int MODE>
+__global__ void __launch_bounds__(192, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               GemmEpilogue ep, int K, uint32_t idesc) {
+  using Cfg = TcCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bar_base = base + Cfg::STAGES * Cfg::STAGE_BYTES;
+  // full[s] at bar_base + 8*s, empty[s] at bar_base + 8*(STAGES+s), acc at + 16*STAGES
+  const uint32_t bar_acc = bar_base + 16 * Cfg::STAGES;
+  volatile uint32_t* tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 16 * Cfg::STAGES + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_blk = blockIdx.x, m_blk = blockIdx.y;
+  const int num_k = K / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(bar_base + 8 * s, 1);
+      mbar_init(bar_base + 8 * (Cfg::STAGES + s), 1);
+    }
+    mbar_init(bar_acc, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer ----
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < num_k; ++kb) {
+        const int s = kb % Cfg::STAGES;
+        const uint32_t ph = (kb / Cfg::STAGES) & 1;
+        if (!mbar_wait_bounded(bar_base + 8 * (Cfg::STAGES + s), ph ^ 1)) {
+          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_MMA);
+          *abort_flag = 1;
+          break;
+        }
+        if (*abort_flag) break;
+        const uint32_t full = bar_base + 8 * s;
+        const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(full, Cfg::STAGE_BYTES);
+        tma_load_2d(a_dst, &tmap_a, kb * TC_BK, m_blk * TC_BM, full);
+        tma_load_2d(a_dst + Cfg::A_BYTES, &tmap_b, kb * TC_BK, n_blk * BN, full);
+        ++issued;
+      }
+      (void)issued;
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = 0; kb < num_k; ++kb) {
+        const int s = kb % Cfg::STAGES;
+        const uint32_t ph = (kb / Cfg::STAGES) & 1;
+        if (!mbar_wait_bounded(bar_base + 8 * s, ph)) {
+          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = base + s * Cfg::STAGE_BYTES;
+        const uint64_t da = umma_desc_k_sw128(a_addr);
+        const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+          // +32 bytes per K step of 16 elements -> +2 in the (addr >> 4) field
+          umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) ? 1u : 0u);
+        }
+        umma_commit(bar_base + 8 * (Cfg::STAGES + s));  // frees the stage when the MMAs retire
+      }
+      if (ok) umma_commit(bar_acc);
+    }
+  } else {
+    // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int m = m_blk * TC_BM + row_in_tile;
+    const bool row_ok = m < ep.M;
+    bool ok = mbar_wait_bounded(bar_acc, 0);
+    if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      RopeRow rr;
+      rr.x = rr.y = rr.z = 0;
+      rr.kv_row = -1;
+      if (MODE == EPI_QKV_ROPE && row_ok) rr = rope_row_ctx(ep, m);
+      if constexpr (MODE == EPI_SWIGLU) {
+        // gate columns [0,64) and up columns [64,128) of every 128-column group
+#pragma unroll 1
+        for (int g0 = 0; g0 < BN; g0 += 128) {
+#pragma unroll 1
+          for (int c = 0; c < 2; ++c) {
+            uint32_t rg[32], ru[32];
+            tmem_ld_32x32(t_row + g0 + c * 32, rg);
+            tmem_ld_32x32(t_row + g0 + 64 + c * 32, ru);
+            tmem_wait_ld();
+            if (row_ok) {
+              const int n0 = n_blk * BN + g0 + c * 32;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                const float4 g = make_float4(__uint_as_float(rg[4 * q]), __uint_as_float(rg[4 * q + 1]),
+                                             __uint_as_float(rg[4 * q + 2]), __uint_as_float(rg[4 * q + 3]));
+                const float4 u = make_float4(__uint_as_float(ru[4 * q]), __uint_as_float(ru[4 * q + 1]),
+                                             __uint_as_float(ru[4 * q + 2]), __uint_as_float(ru[4 * q + 3]));
+                epi_swiglu_quad(ep, m, n0 + 4 * q, g, u);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_wait_ld();
+          if (row_ok) {
+            const int n0 = n_blk * BN + c * 32;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+              const int n = n0 + 4 * q;
+              if constexpr (MODE == EPI_QKV_ROPE) epi_qkv_quad(ep, rr, m, n, v);
+              else if constexpr (MODE == EPI_RESID) epi_resid_quad(ep, m, n, v);
+              else epi_store_quad(ep, m, n, v);
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, BN);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CUDA-core kernel: 32 x 128 x 32 tiles, 256 threads, each thread 2 rows x (4 + 4) columns
+// (columns c..c+3 and c+64..c+67 so that the SwiGLU partner columns meet in one thread).
+// ---------------------------------------------------------------------------
+constexpr int SM_BM = 32, SM_BN = 128, SM_BK = 32;
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+gemm_simt_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ W, GemmEpilogue ep,
+                 int K, int a_f16) {
+  __shared__ float As[SM_BK][SM_BM + 1];
+  __shared__ __align__(16) float Ws[SM_BK][SM_BN + 4];
+  const int tid = threadIdx.x;
+  const int tx = tid & 15, ty = tid >> 4;
+  const int m0 = blockIdx.y * SM_BM, n0 = blockIdx.x * SM_BN;
+  float acc[2][8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  const int a_row = tid >> 3, a_kq = (tid & 7) * 4;
+  const int w_n = tid >> 1, w_kh = (tid & 1) * 16;
+  for (int k0 = 0; k0 < K; k0 += SM_BK) {
+    {
+      uint2 raw = make_uint2(0u, 0u);
+      if (m0 + a_row < ep.M)
+        raw = *reinterpret_cast<const uint2*>(A + (size_t)(m0 + a_row) * K + k0 + a_kq);
+      const float2 f0 = unpack2_act(raw.x, a_f16), f1 = unpack2_act(raw.y, a_f16);
+      As[a_kq + 0][a_row] = f0.x;
+      As[a_kq + 1][a_row] = f0.y;
+      As[a_kq + 2][a_row] = f1.x;
+      As[a_kq + 3][a_row] = f1.y;
+    }
+    {
+      const uint4* src = reinterpret_cast<const uint4*>(W + (size_t)(n0 + w_n) * K + k0 + w_kh);
+      const uint4 r0 = __ldg(src), r1 = __ldg(src + 1);
+      const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float2 f = unpack2_bf16(w[j]);
+        Ws[w_kh + 2 * j][w_n] = f.x;
+        Ws[w_kh + 2 * j + 1][w_n] = f.y;
+      }
+    }
+    __syncthreads();
+#pragma unroll 8
+    for (int k = 0; k < SM_BK; ++k) {
+      const float a0 = As[k][2 * ty], a1 = As[k][2 * ty + 1];
+      const float4 wl = *reinterpret_cast<const float4*>(&Ws[k][4 * tx]);
+      const float4 wh = *reinterpret_cast<const float4*>(&Ws[k][64 + 4 * tx]);
+      acc[0][0] += a0 * wl.x; acc[0][1] += a0 * wl.y; acc[0][2] += a0 * wl.z; acc[0][3] += a0 * wl.w;
+      acc[0][4] += a0 * wh.x; acc[0][5] += a0 * wh.y; acc[0][6] += a0 * wh.z; acc[0][7] += a0 * wh.w;
+      acc[1][0] += a1 * wl.x; acc[1][1] += a1 * wl.y; acc[1][2] += a1 * wl.z; acc[1][3] += a1 * wl.w;
+      acc[1][4] += a1 * wh.x; acc[1][5] += a1 * wh.y; acc[1][6] += a1 * wh.z; acc[1][7] += a1 * wh.w;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int m = m0 + 2 * ty + i;
+    if (m >= ep.M) continue;
+    const float4 lo = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    const float4 hi = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    const int n = n0 + 4 * tx;
+    if constexpr (MODE == EPI_SWIGLU) {
+      epi_swiglu_quad(ep, m, n, lo, hi);
+    } else if constexpr (MODE == EPI_QKV_ROPE) {
+      const RopeRow rr = rope_row_ctx(ep, m);
+      epi_qkv_quad(ep, rr, m, n, lo);
+      epi_qkv_quad(ep, rr, m, n + 64, hi);
+    } else if constexpr (MODE == EPI_RESID) {
+      epi_resid_quad(ep, m, n, lo);
+      epi_resid_quad(ep, m, n + 64, hi);
+    } else {
+      epi_store_quad(ep, m, n, lo);
+      epi_store_quad(ep, m, n + 64, hi);
+    }
+  }
+}
+
+// ---- host: tensor maps -------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+}  // namespace
+
+int arcb_make_tmap_2d_16b(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,
+                          uint32_t box_rows, uint32_t box_cols, int is_f16) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -100;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {cols * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, is_f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(ptr), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return (int)r;
+}
+
+bool arcb_gemm_tc_supported(int M, int N, int K) {
+  (void)M;
+  return (N % 128 == 0) && (K % 64 == 0) && K >= 64;
+}
+
+template <int MODE>
+static cudaError_t set_tc_smem_attr() {
+  return cudaFuncSetAttribute(gemm_tc_kernel<128, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              TcCfg<128>::SMEM_BYTES);
+}
+
+// Opt in to the large dynamic shared memory of every tcgen05 instantiation (call once, outside
+// any stream capture).
+int arcb_gemm_init() {
+  cudaError_t e;
+  if ((e = set_tc_smem_attr<EPI_STORE_F32>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc_smem_attr<EPI_QKV_ROPE>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc_smem_attr<EPI_RESID>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc_smem_attr<EPI_SWIGLU>()) != cudaSuccess) return (int)e;
+  return get_encode_fn() ? 0 : -100;
+}
+
+template <int MODE>
+static int launch_gemm_mode(const void* a16, const void* w_bf16, const GemmEpilogue& ep, int K,
+                            int act_f16, bool use_tc, cudaStream_t stream) {
+  const int M = ep.M, N = ep.N;
+  if (use_tc) {
+    constexpr int BN = 128;
+    CUtensorMap ta, tb;
+    int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
+    if (r) return 1000 + r;
+    r = arcb_make_tmap_2d_16b(&tb, w_bf16, (uint64_t)N, (uint64_t)K, BN, TC_BK, 0);
+    if (r) return 1000 + r;
+    const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, 1);
+    dim3 grid(N / BN, (M + TC_BM - 1) / TC_BM);
+    gemm_tc_kernel<BN, MODE><<<grid, 192, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc);
+  } else {
+    dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
+    gemm_simt_kernel<MODE><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a16),
+                                                     reinterpret_cast<const uint16_t*>(w_bf16), ep, K,
+                                                     act_f16);
+  }
+  arcb_count_launch(1);
+  return (int)cudaGetLastError();
+}
+
+int arcb_launch_gemm(const void* a16, const void* w_bf16, const GemmEpilogue& ep, int K, int act_f16,
+                     bool use_tc, cudaStream_t stream) {
+  const int M = ep.M, N = ep.N;
+  if (M <= 0) return 0;
+  if (N % 128 != 0 || K % 32 != 0) return -1;
+  if (use_tc && !arcb_gemm_tc_supported(M, N, K)) return -1;
+  switch (ep.mode) {
+    case EPI_STORE_F32: return launch_gemm_mode<EPI_STORE_F32>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
+    case EPI_QKV_ROPE: return launch_gemm_mode<EPI_QKV_ROPE>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
+    case EPI_RESID: return launch_gemm_mode<EPI_RESID>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
+    case EPI_SWIGLU: return launch_gemm_mode<EPI_SWIGLU>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
+  }
+  return -1;
+}

@@ -1,0 +1,195 @@
+"""Token codec, 3D positions and augmentation primitives (host side of the hot path).
+
+Same vocabulary and rules as the reference's ``src/data.py:26-305``: 14 tokens
+(colours 0-9, START 10, NEWLINE 11, IO_SEP 12, END 13), row-major grids with a NEWLINE
+after every row, 3D positions (x column, y row, z layer), the 8 dihedral transforms in
+the reference's order and its seeded colour permutations.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+VOCAB_SIZE = 14
+START_TOKEN_ID = 10
+NEWLINE_TOKEN_ID = 11
+IO_SEP_TOKEN_ID = 12
+END_TOKEN_ID = 13
+PAD_TOKEN_ID = END_TOKEN_ID
+
+MAX_X = 30  # largest x position the grid-state rules produce (src/data.py:126)
+MAX_Y = 29  # largest y position (src/data.py:127)
+
+Grid = list  # list[list[int]]
+
+
+# ---------------------------------------------------------------------------
+# token codec (src/data.py:40-117)
+# ---------------------------------------------------------------------------
+def grid_to_tokens(grid: Grid) -> list[int]:
+    out: list[int] = []
+    for row in grid:
+        out += list(row)
+        out.append(NEWLINE_TOKEN_ID)
+    return out
+
+
+def tokens_to_grid(tokens) -> Grid:
+    rows: Grid = []
+    cur: list[int] = []
+    for t in tokens:
+        t = int(t)
+        if t == NEWLINE_TOKEN_ID:
+            if cur:
+                rows.append(cur)
+                cur = []
+        elif t < 10:
+            cur.append(t)
+        # START / IO_SEP / END inside an output are dropped
+    if cur:
+        rows.append(cur)
+    return rows
+
+
+def encode_example(input_grid: Grid, output_grid: Grid | None = None) -> list[int]:
+    toks = [START_TOKEN_ID] + grid_to_tokens(input_grid) + [IO_SEP_TOKEN_ID]
+    if output_grid is not None:
+        toks += grid_to_tokens(output_grid) + [END_TOKEN_ID]
+    return toks
+
+
+def decode_output_grid(tokens) -> Grid | None:
+    """Grid between the first IO_SEP of ``tokens`` and the next END; None if absent/empty."""
+    toks = [int(t) for t in tokens]
+    if IO_SEP_TOKEN_ID not in toks:
+        return None
+    start = toks.index(IO_SEP_TOKEN_ID) + 1
+    stop = len(toks)
+    for i in range(start, len(toks)):
+        if toks[i] == END_TOKEN_ID:
+            stop = i
+            break
+    body = toks[start:stop]
+    if not body:
+        return None
+    return tokens_to_grid(body)
+
+
+# ---------------------------------------------------------------------------
+# 3D positions (src/data.py:124-175)
+# ---------------------------------------------------------------------------
+def compute_positions_3d(tokens, max_x: int = MAX_X, max_y: int = MAX_Y) -> np.ndarray:
+    n = len(tokens)
+    pos = np.zeros((n, 3), dtype=np.int64)
+    x = y = 0
+    in_output = False
+    for i in range(n):
+        t = int(tokens[i])
+        if t == START_TOKEN_ID:
+            x = y = 0
+            in_output = False  # position stays (0, 0, 0)
+        elif t == NEWLINE_TOKEN_ID:
+            pos[i, 1] = y
+            pos[i, 2] = 3 if in_output else 1
+            x = 0
+            y = min(y + 1, max_y)
+        elif t == IO_SEP_TOKEN_ID:
+            pos[i, 2] = 2
+            x = y = 0
+            in_output = True
+        elif t == END_TOKEN_ID:
+            pos[i, 2] = 4
+        else:
+            pos[i, 0] = min(x, max_x)
+            pos[i, 1] = min(y, max_y)
+            pos[i, 2] = 3 if in_output else 1
+            x += 1
+    return pos
+
+
+# ---------------------------------------------------------------------------
+# dihedral group (src/data.py:182-233); index order is part of the contract
+# ---------------------------------------------------------------------------
+def _transposed(grid: Grid) -> Grid:
+    """Columns of ``grid`` as rows, truncated to the shortest row (zip semantics)."""
+    if not grid:
+        return []
+    width = min(len(r) for r in grid)
+    return [[grid[i][j] for i in range(len(grid))] for j in range(width)]
+
+
+def identity(grid: Grid) -> Grid:
+    return [list(r) for r in grid]
+
+
+def rot90(grid: Grid) -> Grid:  # clockwise
+    return _transposed(grid[::-1])
+
+
+def rot180(grid: Grid) -> Grid:
+    return [list(r)[::-1] for r in grid[::-1]]
+
+
+def rot270(grid: Grid) -> Grid:
+    return _transposed(grid)[::-1]
+
+
+def flip_h(grid: Grid) -> Grid:
+    return [list(r)[::-1] for r in grid]
+
+
+def flip_v(grid: Grid) -> Grid:
+    return [list(r) for r in grid[::-1]]
+
+
+def flip_diag(grid: Grid) -> Grid:
+    return _transposed(grid)
+
+
+def flip_anti_diag(grid: Grid) -> Grid:
+    return [r[::-1] for r in _transposed(grid)[::-1]]
+
+
+DIHEDRAL_TRANSFORMS = [identity, rot90, rot180, rot270, flip_h, flip_v, flip_diag, flip_anti_diag]
+# DIHEDRAL_TRANSFORMS[INVERSE_DIHEDRAL[i]] undoes DIHEDRAL_TRANSFORMS[i] (src/voting.py:16)
+INVERSE_DIHEDRAL = [0, 3, 2, 1, 4, 5, 6, 7]
+# transforms that swap height and width (src/inference.py:274-282)
+TRANSPOSING = frozenset({1, 3, 6, 7})
+
+
+def apply_dihedral_transform(input_grid: Grid, output_grid: Grid, transform_idx: int):
+    f = DIHEDRAL_TRANSFORMS[transform_idx]
+    return f(input_grid), f(output_grid)
+
+
+def inverse_dihedral(grid: Grid, transform_idx: int) -> Grid:
+    return DIHEDRAL_TRANSFORMS[INVERSE_DIHEDRAL[transform_idx]](grid)
+
+
+# ---------------------------------------------------------------------------
+# colour permutations (src/data.py:257-305)
+# ---------------------------------------------------------------------------
+def generate_color_permutations(n_perms: int, seed: int = 42) -> np.ndarray:
+    """[n_perms, 10] old->new colour maps; row 0 is the identity, colour 0 is fixed.
+
+    Draws ``default_rng(seed).permutation(arange(1, 10))`` once per further row, which is the
+    stream the reference consumes, so the permutations are identical for a given seed.
+    """
+    rng = np.random.default_rng(seed)
+    perms = np.zeros((n_perms, 10), dtype=np.int64)
+    if n_perms > 0:
+        perms[0] = np.arange(10)
+    for i in range(1, n_perms):
+        perms[i, 1:] = rng.permutation(np.arange(1, 10))
+    return perms
+
+
+def inverse_color_perm(perm) -> np.ndarray:
+    perm = np.asarray(perm)
+    inv = np.zeros_like(perm)
+    inv[perm] = np.arange(len(perm))
+    return inv
+
+
+def apply_color_perm_grid(grid: Grid, perm) -> Grid:
+    lut = [int(v) for v in perm]
+    return [[lut[c] for c in row] for row in grid]

@@ -1,0 +1,258 @@
+"""Drop-in for the reference's generation API (``src/inference.py``) on the B200 engine.
+
+``generate_output`` and ``predict_with_augmentations`` keep the reference's signatures, argument
+meaning and error behaviour; only greedy, unconstrained decoding is implemented natively
+(sampling and soft constraints raise ``NotImplementedError`` rather than falling back).
+
+Differences from the reference that are part of the design:
+  * prompts are packed (no padded positions are computed) and the KV cache is compacted, which
+    is exact because attention is permutation-invariant over keys and positions enter only
+    through the (x, y, z) RoPE;
+  * a row that has emitted END is frozen and keeps emitting END, whereas the reference keeps
+    sampling from such rows until every row has finished; rows agree through their first END.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import numpy as np
+import torch
+
+from .data import (DIHEDRAL_TRANSFORMS, END_TOKEN_ID, IO_SEP_TOKEN_ID, apply_color_perm_grid,
+                   compute_positions_3d, decode_output_grid, encode_example, generate_color_permutations)
+from .engine import Engine, Session, chunk_rows, engine_for, plan_prefill
+
+DEFAULT_PREFILL_TOKENS = 65536  # packed prompt tokens per prefill call (bounds the workspace)
+POLL_EVERY = 32                 # decode steps between two host checks of the finished counter
+
+
+@dataclass(frozen=True)
+class DecodingConstraints:
+    """Placeholder with the reference's fields (src/inference.py:36-43); not implemented natively."""
+    palette_mask: torch.Tensor | None = None
+    target_shape: torch.Tensor | None = None
+    palette_penalty: float = 2.0
+    shape_penalty: float = 2.0
+    disallow_tokens: tuple = (10, 12)
+
+
+@dataclass
+class GenerationTrace:
+    """Extra outputs of ``generate_tokens`` used by the parity harness and the benchmark."""
+    tokens: torch.Tensor                 # int32 [B, n_generated] on the device
+    first_logits: torch.Tensor | None    # fp32 [B, 14]
+    step_logits: torch.Tensor | None     # fp32 [B, max_new, 14]
+    prefill_tokens: int = 0
+    decode_steps: int = 0
+    h2d_bytes: int = 0
+
+
+def _resolve_engine(model, device) -> Engine:
+    """Engine for ``model``: on ``device`` if it is a CUDA device, else where the model lives,
+    else the current CUDA device.  Raises when no CUDA device exists (there is no CPU path)."""
+    if isinstance(model, Engine):
+        return model
+    if device is not None and torch.device(device).type == "cuda":
+        return engine_for(model, device=device)
+    p = next(model.parameters(), None)
+    if p is not None and p.device.type == "cuda":
+        return engine_for(model, device=p.device)
+    if not torch.cuda.is_available():
+        raise RuntimeError("mdlarc_scale_b200 needs a B200 GPU: no CUDA device is available and "
+                           "there is no CPU fallback")
+    return engine_for(model, device=torch.device("cuda", torch.cuda.current_device()))
+
+
+def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.ndarray,
+                    example_ids: np.ndarray | None, max_new: int, stop_on_end: bool = True,
+                    forced: np.ndarray | None = None, want_logits: bool = False,
+                    max_prefill_tokens: int = DEFAULT_PREFILL_TOKENS, attn_splits: int = 0,
+                    session: Session | None = None, pinned: bool = False) -> GenerationTrace:
+    """Prefill + greedy decode of a padded batch given as host arrays; returns device tokens.
+
+    ``ids`` int [B, S], ``pos`` int [B, S, 3], ``mask`` bool [B, S] (True = real token).  At most
+    ``max_new`` tokens are generated per row.  ``forced`` ([B, max_new]) teacher-forces the fed
+    tokens while logits and argmax are still produced for every step.
+    """
+    dev = engine.device
+    B, S = ids.shape
+    lens = mask.sum(axis=1)
+    t_max = int(lens.max()) + int(max_new)
+    cap = int(min(max_prefill_tokens, int(lens.sum()) + 2 * B))
+    cap = max(cap, int(lens.max()) + 2, B)
+    if session is None:
+        session = engine.new_session(
+            B, t_max, max_new, cap, stop_on_end=stop_on_end, attn_splits=attn_splits,
+            forced=None if forced is None else torch.from_numpy(np.ascontiguousarray(forced, dtype=np.int32)),
+            want_step_logits=want_logits)
+    ex_dev = None
+    h2d = 0
+    if example_ids is not None and engine.use_example_embedding:
+        ex_host = torch.from_numpy(np.ascontiguousarray(example_ids, dtype=np.int32))
+        if pinned:
+            ex_host = ex_host.pin_memory()
+        ex_dev = ex_host.to(dev, non_blocking=True)
+        h2d += ex_host.numel() * 4
+    first_logits = torch.zeros((B, 14), dtype=torch.float32, device=dev) if want_logits else None
+    n_prefill = 0
+    for rows in chunk_rows(lens, session.max_prefill_tokens):
+        plan = plan_prefill(ids, pos, mask, rows)
+        h2d += plan.h2d_bytes()
+        n_prefill += plan.n_tokens
+        fl = None
+        if first_logits is not None:
+            fl = torch.zeros((len(rows), 14), dtype=torch.float32, device=dev)
+        session.prefill(plan.to(dev), ex_dev, first_logits=fl)
+        if fl is not None:
+            first_logits[torch.from_numpy(rows).to(dev)] = fl
+    steps_total = max_new - 1
+    done = 0
+    while done < steps_total:
+        n = min(POLL_EVERY, steps_total - done) if stop_on_end and forced is None else steps_total - done
+        session.decode(n)
+        done += n
+        if stop_on_end and forced is None and done < steps_total and session.poll() >= B:
+            break
+    session.poll()  # synchronise and surface any device-side error word
+    n_gen = done + 1
+    toks = session.out_tokens[:, :n_gen]
+    if stop_on_end and forced is None:
+        # the reference stops as soon as every row has emitted END (src/inference.py:594)
+        is_end = toks == END_TOKEN_ID
+        if bool(is_end.any(dim=1).all()):
+            first_end = is_end.to(torch.int32).argmax(dim=1)
+            n_gen = int(first_end.max().item()) + 1
+            toks = toks[:, :n_gen]
+    return GenerationTrace(tokens=toks, first_logits=first_logits, step_logits=session.step_logits,
+                           prefill_tokens=n_prefill, decode_steps=done, h2d_bytes=h2d)
+
+
+def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
+                    example_ids: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None,
+                    max_new_tokens: int = 900, temperature: float = 0.0, top_k: int | None = None,
+                    stop_on_end: bool = True, use_compile: bool = False, constraints=None) -> torch.Tensor:
+    """Greedy generation with a static KV cache; same contract as ``src/inference.py:487-628``.
+
+    ``model`` is a reference ``TinyTransformer`` (its weights are packed once and cached) or an
+    ``Engine``.  Returns ``[batch, seq_len + n_generated]`` int64 on ``input_ids.device``.
+    ``use_compile`` is accepted and ignored: the decode step always runs as a CUDA graph.
+    """
+    if temperature > 0:
+        raise NotImplementedError("sampling (temperature > 0) is not implemented on the B200 path")
+    if constraints is not None:
+        raise NotImplementedError("soft decoding constraints are not implemented on the B200 path")
+    batch, prompt_len = input_ids.shape
+    if attention_mask is not None and tuple(attention_mask.shape) != (batch, prompt_len):
+        raise ValueError("attention_mask must have shape [batch, seq_len]")
+    if isinstance(model, Engine):
+        engine = model
+    else:
+        model.eval()
+        engine = _resolve_engine(model, input_ids.device)
+    max_total = min(prompt_len + max_new_tokens, engine.max_seq_len)
+    max_new = max_total - prompt_len
+    if max_new <= 0:
+        return input_ids
+    ids = input_ids.detach().cpu().numpy()
+    pos = positions_3d.detach().cpu().numpy()
+    mask = (np.ones((batch, prompt_len), dtype=bool) if attention_mask is None
+            else attention_mask.detach().to(torch.bool).cpu().numpy())
+    ex = (np.zeros(batch, dtype=np.int64) if example_ids is None else example_ids.detach().cpu().numpy())
+    trace = generate_tokens(engine, ids, pos, mask, ex, max_new, stop_on_end=stop_on_end)
+    gen = trace.tokens.to(device=input_ids.device, dtype=input_ids.dtype)
+    return torch.cat([input_ids, gen], dim=1)
+
+
+def _grid_after_last_sep(tokens: list[int]):
+    seps = [i for i, t in enumerate(tokens) if t == IO_SEP_TOKEN_ID]
+    return decode_output_grid(tokens[seps[-1]:]) if seps else None
+
+
+def build_augmented_prompts(task: dict, test_idx: int, use_train_examples: bool = True,
+                            num_color_perms: int = 8, num_samples: int = 1):
+    """All (dihedral x colour-permutation x sample) prompts of one test input, in the reference's
+    candidate order (src/inference.py:794-827): dihedral-major, then permutation, then sample.
+
+    Returns ``(prompts, positions, aug_info)`` with ``aug_info[i] = (dihedral_idx, perm_tuple|None)``.
+    """
+    train_pairs = task["train"] if use_train_examples else []
+    test_input = task["test"][test_idx]["input"]
+    perms = generate_color_permutations(num_color_perms, seed=42)
+    prompts, positions, info = [], [], []
+    for d_idx, fn in enumerate(DIHEDRAL_TRANSFORMS):
+        ins = [fn(p["input"]) for p in train_pairs]
+        outs = [fn(p["output"]) for p in train_pairs]
+        tst = fn(test_input)
+        for p_idx in range(num_color_perms):
+            perm = perms[p_idx]
+            if p_idx > 0:
+                p_ins = [apply_color_perm_grid(g, perm) for g in ins]
+                p_outs = [apply_color_perm_grid(g, perm) for g in outs]
+                p_tst = apply_color_perm_grid(tst, perm)
+                tag = tuple(int(v) for v in perm)
+            else:
+                p_ins, p_outs, p_tst, tag = ins, outs, tst, None
+            if len(p_ins) != len(p_outs):
+                raise ValueError("train inputs and outputs differ in number")
+            toks: list[int] = []
+            for gi, go in zip(p_ins, p_outs):
+                toks += encode_example(gi, go)
+            toks += encode_example(p_tst, None)
+            pos = compute_positions_3d(toks)
+            for _ in range(max(1, num_samples)):
+                prompts.append(toks)
+                positions.append(pos)
+                info.append((d_idx, tag))
+    return prompts, positions, info
+
+
+def pad_prompts(prompts, positions, left: bool = True):
+    """Pad ragged prompts to one length with END / (0,0,0) (src/inference.py:878-890)."""
+    n = len(prompts)
+    width = max(len(p) for p in prompts)
+    ids = np.full((n, width), END_TOKEN_ID, dtype=np.int64)
+    pos = np.zeros((n, width, 3), dtype=np.int64)
+    mask = np.zeros((n, width), dtype=bool)
+    for i, (p, q) in enumerate(zip(prompts, positions)):
+        k = len(p)
+        sl = slice(width - k, width) if left else slice(0, k)
+        ids[i, sl] = p
+        pos[i, sl] = q
+        mask[i, sl] = True
+    return ids, pos, mask
+
+
+def predict_with_augmentations(model, task: dict, test_idx: int, device, example_id: int = 0,
+                               use_train_examples: bool = True, num_color_perms: int = 8,
+                               max_output_tokens: int = 900, num_samples: int = 1,
+                               sample_temperature: float = 0.0, sample_top_k: int | None = None,
+                               constrain_decoding: bool = False, palette_penalty: float = 2.0,
+                               shape_penalty: float = 2.0, batched: bool = True, use_compile: bool = False,
+                               max_batch_size: int = 16):
+    """Candidates under all augmentations for AAIVR voting (``src/inference.py:697-920``).
+
+    Returns ``[(grid | None, dihedral_idx, colour_perm | None), ...]`` in the reference's order.
+    Chunks of ``max_batch_size`` left-padded prompts go through ``generate_output`` exactly as the
+    reference's batched path does, so each chunk reproduces its semantics (including which
+    hidden state yields the first token of a left-padded row).
+    """
+    if sample_temperature > 0 or constrain_decoding:
+        raise NotImplementedError("sampling / constrained decoding are not implemented on the B200 path")
+    device = torch.device(device)
+    engine = _resolve_engine(model, device)
+    prompts, positions, info = build_augmented_prompts(task, test_idx, use_train_examples,
+                                                       num_color_perms, num_samples)
+    out = []
+    for c0 in range(0, len(prompts), max_batch_size):
+        chunk = slice(c0, min(c0 + max_batch_size, len(prompts)))
+        ids, pos, mask = pad_prompts(prompts[chunk], positions[chunk], left=True)
+        ids_t = torch.from_numpy(ids).to(device)
+        full = generate_output(engine, ids_t, torch.from_numpy(pos).to(device),
+                               torch.full((ids.shape[0],), example_id, dtype=torch.long, device=device),
+                               attention_mask=torch.from_numpy(mask).to(device),
+                               max_new_tokens=max_output_tokens, stop_on_end=True)
+        rows = full.cpu().tolist()
+        for i, toks in enumerate(rows):
+            d_idx, tag = info[c0 + i]
+            out.append((_grid_after_last_sep(toks), d_idx, tag))
+    return out
