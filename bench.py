@@ -1,0 +1,350 @@
+#!/usr/bin/env python
+"""Benchmark of the hot path: batched greedy generation of the large TinyTransformer, bf16.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the decode-bound large configuration): `--batch` sequences per GPU per step with short
+prompts (2 train pairs + test input, grids 3..10 x 3..10), END suppressed, every sequence decoded
+for the full 931-token budget over a static KV cache of 1536 positions.  One step = one pass of
+the hot path over one such batch: packed prefill + 930 graph-replayed decode steps.  Under
+torchrun every rank runs its own batch (weak scaling, no data-path collective).
+
+Prints ONE JSON line (rank 0): generated tokens/s over all GPUs, device-timed (`value`, inputs
+resident in HBM) and end to end through `generate_output` from pinned host tensors (`e2e`),
+plus the roofline of the dominant kernel (decode attention, HBM-bound), the CPU baseline, clocks.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+MAX_NEW = 931
+KV_POSITIONS = 1536
+MODEL_SIZE = "large"
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.rows = []
+        self._stop = threading.Event()
+        self._t = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
+                parts = [x.strip() for x in out.stdout.strip().split(",")]
+                if len(parts) >= 7:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        self._t.join(timeout=6)
+
+    def summary(self):
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        sm = sorted(float(r[0]) for r in self.rows)
+        reasons = []
+        for i, name in enumerate(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")):
+            if any(r[3 + i].lower().startswith("active") for r in self.rows):
+                reasons.append(name)
+        return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": float(self.rows[0][1]), "reasons": reasons,
+                "samples": len(self.rows)}
+
+
+def make_batch(seed: int, n: int):
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import pad_prompts
+    tasks = synthetic.capped_tasks(seed, n, 2, 2, 3, 10, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    return pad_prompts(prompts, positions, left=False)
+
+
+def model_state():
+    from oracle import arc_model as om  # weight initialiser only (seeded random-init, reference distributions)
+    cfg = om.make_config(MODEL_SIZE, max_seq_len=4096)
+    return cfg, om.round_bf16(om.init_state(cfg, seed=0))
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline / reference arm: the oracle port of generate_output on the host cores
+# ---------------------------------------------------------------------------
+def cpu_generate_sample(n_seqs: int, n_steps: int, seed: int):
+    from oracle import arc_model as om
+    cfg, sd = model_state()
+    ids, pos, mask = make_batch(seed, n_seqs)
+    t0 = time.perf_counter()
+    r = om.generate(sd, cfg, torch.from_numpy(ids), torch.from_numpy(pos), None, torch.from_numpy(mask),
+                    max_new_tokens=n_steps, stop_on_end=False)
+    dt = time.perf_counter() - t0
+    gen = r.tokens.shape[1] - ids.shape[1]
+    return n_seqs * gen / dt, dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    n_seqs, n_steps = args.cpu_seqs, args.cpu_steps
+    for i in range(args.warmup):
+        cpu_generate_sample(2, 4, 1000 + i)
+    vals, times = [], []
+    for i in range(args.steps):
+        v, dt = cpu_generate_sample(n_seqs, n_steps, 2000 + i)
+        vals.append(v)
+        times.append(dt)
+    value = float(np.mean(vals))
+    sample = (f"{n_seqs} sequences of the same generator, prefill + {n_steps} greedy tokens each per step, "
+              f"fp32, oracle port of generate_output (tokens / wall time incl. prefill)")
+    line = {
+        "impl": "reference", "metric": "generated tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1000 * float(np.mean(times)), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "cfg4-large-decode (bounded CPU sample)", "model": MODEL_SIZE},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------
+def attention_roofline(engine, session, lens0: np.ndarray, n_layers_sampled: int = 2):
+    """Replays the decode-attention kernel on the live KV cache at five points of the decode
+    trajectory (same launch shape as inside the graph) and times each launch with CUDA events."""
+    import ctypes as C
+    from mdlarc_scale_b200 import _lib
+    lib = engine.lib
+    B, H, T = session.n_seqs, engine.n_heads, session.t_max
+    dev = engine.device
+    q = torch.randn(B, H, 64, device=dev).to(torch.float16)
+    out = torch.empty_like(q)
+    layer_bytes = 2 * B * engine.d_model * T * 2
+    times, bytes_ = [], []
+    for frac in (0.05, 0.25, 0.5, 0.75, 1.0):
+        lens = torch.from_numpy((lens0 + int(frac * (MAX_NEW - 1))).astype(np.int32)).to(dev)
+        algo = int(lens.sum().item()) * H * 64 * 2 * 2  # K and V rows, bf16, each read once
+        for layer in range(n_layers_sampled):
+            kptr = session.kv_cache.data_ptr() + layer * layer_bytes
+            vptr = kptr + layer_bytes // 2
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(lib.arcb_op_decode_attention(q.data_ptr(), kptr, vptr, out.data_ptr(), None, lens.data_ptr(),
+                                                    None, B, H, T, 1, None, _lib.ACT_F16,
+                                                    torch.cuda.current_stream(dev).cuda_stream))
+            e1.record()
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1) / 1e3)
+            bytes_.append(algo)
+    gbs = float(np.mean([b / t for b, t in zip(bytes_, times)]) / 1e9)
+    return gbs, float(np.mean(times) * 1e3), float(np.mean(bytes_))
+
+
+def run_ours(args, rank, world, local_rank):
+    from mdlarc_scale_b200 import _lib
+    from mdlarc_scale_b200.engine import Engine, chunk_rows, plan_prefill
+    from mdlarc_scale_b200.inference import generate_output
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    cfg, sd = model_state()
+    engine = Engine(sd, cfg, dev)
+    lib = engine.lib
+    B = args.batch
+    n_total = args.warmup + args.steps
+    batches = [make_batch(10_000 * rank + i, B) for i in range(n_total)]
+    prefill_cap = 65536
+    session = engine.new_session(B, KV_POSITIONS, MAX_NEW, prefill_cap, stop_on_end=False)
+
+    def upload(batch):
+        ids, pos, mask = batch
+        lens = mask.sum(axis=1)
+        return [plan_prefill(ids, pos, mask, rows).to(dev) for rows in chunk_rows(lens, prefill_cap)], lens
+
+    def device_step(plans):
+        for p in plans:
+            session.prefill(p, None)
+        session.decode(MAX_NEW - 1)
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    # ---- device-timed value: inputs resident in HBM ----
+    resident = [upload(b) for b in batches]
+    for i in range(args.warmup):
+        device_step(resident[i][0])
+    session.poll()
+    barrier()
+    lib.arcb_launch_count(1)
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with sampler:
+        e0.record()
+        for i in range(args.warmup, n_total):
+            device_step(resident[i][0])
+        e1.record()
+        barrier()
+    launches = int(lib.arcb_launch_count(0))
+    session.poll()
+    dt = e0.elapsed_time(e1) / 1e3
+    prefill_tokens = int(sum(int(r[1].sum()) for r in resident[args.warmup:]))
+    # prefill share, device-timed on the same inputs (one extra untimed-for-value pass)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record()
+    for p in resident[-1][0]:
+        session.prefill(p, None)
+    p1.record()
+    p1.synchronize()
+    prefill_s = p0.elapsed_time(p1) / 1e3
+    prefill_tok_s = int(resident[-1][1].sum()) / prefill_s
+    session.decode(8)
+    attn_gbs, attn_ms, attn_bytes = attention_roofline(engine, session, resident[-1][1])
+    lens_last = resident[-1][1]
+    del resident
+
+    # ---- end to end through the public API: pinned host tensors in, host tokens out ----
+    session.close()
+    del session
+    torch.cuda.empty_cache()
+    host = []
+    for ids, pos, mask in batches:
+        host.append((torch.from_numpy(ids).pin_memory(), torch.from_numpy(pos).pin_memory(),
+                     torch.from_numpy(mask).pin_memory()))
+    h2d = d2h = 0
+    for i in range(min(args.warmup, 1)):
+        generate_output(engine, *host[i][:2], None, host[i][2], max_new_tokens=MAX_NEW, stop_on_end=False)
+    barrier()
+    t0 = time.perf_counter()
+    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    g0.record()
+    for i in range(args.warmup, n_total):
+        ids_t, pos_t, mask_t = host[i]
+        out = generate_output(engine, ids_t, pos_t, None, mask_t, max_new_tokens=MAX_NEW, stop_on_end=False)
+        assert out.device.type == "cpu" and out.shape[1] == ids_t.shape[1] + MAX_NEW
+        n_valid = int(mask_t.sum())
+        h2d += n_valid * 4 * 7 + B * 4 * 6  # packed ids, xyz, seq, slot, count (+ per-sequence arrays)
+        d2h += B * MAX_NEW * 4
+    g1.record()
+    barrier()
+    e2e_dt = max(time.perf_counter() - t0, g0.elapsed_time(g1) / 1e3)
+
+    def max_over_ranks(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    dt = max_over_ranks(dt)
+    e2e_dt = max_over_ranks(e2e_dt)
+    gen_tokens = world * args.steps * B * MAX_NEW
+    clocks = sampler.summary()
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        line = {
+            "metric": "generated tokens/s", "value": gen_tokens / dt, "unit": "tokens/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000 * dt / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": "cfg4-large-decode", "model": MODEL_SIZE, "sequences_per_gpu_per_step": B,
+                       "new_tokens": MAX_NEW, "kv_positions": KV_POSITIONS, "stop_on_end": False,
+                       "activations": "f16 operands, bf16 weights + KV cache, f32 accumulate/residual",
+                       "l2": "inputs larger than L2 (KV cache %.1f GB per GPU)" % (B * KV_POSITIONS * engine.kv_bytes_per_position() / 1e9),
+                       "parallelism": f"dp{world} (independent sequence shards)"},
+            "e2e": {"value": gen_tokens / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d // args.steps,
+                    "d2h_bytes_per_step": d2h // args.steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": attn_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": attn_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "kernel": "attn_stream_kernel (decode attention)", "ms_per_launch": attn_ms,
+                         "algorithmic_bytes_per_launch": attn_bytes},
+            "prefill": {"tokens_per_s_per_gpu": prefill_tok_s, "tokens_per_step": prefill_tokens // args.steps},
+        }
+        if not args.no_cpu and world >= 1:
+            torch.set_num_threads(os.cpu_count() or 1)
+            v, cdt = cpu_generate_sample(args.cpu_seqs, args.cpu_steps, 777)
+            line["cpu_baseline"] = {
+                "value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                "sample": f"{args.cpu_seqs} sequences x (prefill + {args.cpu_steps} greedy tokens), fp32 oracle port, "
+                          f"{cdt:.1f} s wall"}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=1024, help="sequences per GPU per step")
+    ap.add_argument("--cpu-seqs", type=int, default=16)
+    ap.add_argument("--cpu-steps", type=int, default=48)
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a B200 GPU (the product path has no CPU fallback)")
+    run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -14,9 +14,7 @@
  *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
  *   - return value: 0 = ok, <0 = argument/state error (ARCB_E_*), >0 = a
  *     cudaError_t / CUresult value; arcb_last_error() gives a message;
- *   - no exceptions cross the boundary, no global state besides the handles
- *     (except the statically allocated scratch of the *_static entry point,
- *     documented there).
+ *   - no exceptions cross the boundary, no global state besides the handles.
  */
 #ifndef ARCB200_H
 #define ARCB200_H
@@ -103,7 +101,8 @@ int arcb_device_ok(void);
 int arcb_engine_create(const arcb_config* cfg, arcb_engine** out);
 int arcb_engine_destroy(arcb_engine* eng);
 
-/* Round one fp32 tensor to bf16 and store it in kernel layout.  `layer` is
+/* Round one fp32 tensor to bf16 (the model precision) and store it in kernel layout; GEMM
+ * weights are held in the 16-bit container selected by act_format.  `layer` is
  * ignored for the model-level kinds.  The copy/convert runs on `stream`. */
 int arcb_engine_load_tensor(arcb_engine* eng, int32_t kind, int32_t layer, const float* d_src,
                             int64_t numel, void* stream);
@@ -154,10 +153,15 @@ typedef struct arcb_prefill_args {
   const int32_t* d_kv_slot;    /* [n_tokens]                                   */
   const int32_t* d_kv_count;   /* [n_tokens]                                   */
   const int32_t* d_example_ids; /* [B] indexed by cache row (NULL = no example embedding) */
-  /* flash-prefill work list: query blocks of <=128 consecutive rows of one sequence */
+  /* tensor-core prefill attention work list (optional; without it the streaming kernel runs):
+   * query blocks of <= 128 consecutive rows of one sequence, and where each row's K/V goes in
+   * the call's contiguous 16-bit K/V scratch (a sequence's keys are consecutive rows in slot order) */
   int32_t n_qblocks;
   const int32_t* d_qblock_row0; /* [n_qblocks] first packed row                */
   const int32_t* d_qblock_rows; /* [n_qblocks] rows in block (1..128)          */
+  const int32_t* d_qblock_kv0;  /* [n_qblocks] first scratch row of the block's sequence */
+  const int32_t* d_kv_row;      /* [n_tokens] scratch row of the token's K/V, < 0: none  */
+  int32_t n_kv_rows;            /* scratch rows written by this call (all in [0, n_kv_rows)) */
   float* d_logits_all;         /* optional [n_tokens][14]                      */
   int32_t n_first;
   const int32_t* d_first_row;  /* [n_first] packed row whose hidden state is read */
@@ -190,10 +194,11 @@ int64_t arcb_launch_count(int reset);
 int arcb_op_rmsnorm(const float* d_x, const float* d_w, void* d_out16, int32_t rows, int32_t d,
                     float eps, int32_t act_format, void* stream);
 
-/* y[M,N] (fp32) = A[M,K] (16-bit, act_format) * W[N,K]^T (bf16): nn.Linear without
- * bias as used at src/inference.py:402,410 / src/transformer.py:260-263.
+/* y[M,N] (fp32) = A[M,K] * W[N,K]^T, A and W both in the 16-bit format `act_format`
+ * (the tensor-core MMA needs one format for both operands): nn.Linear without bias as used
+ * at src/inference.py:402,410 / src/transformer.py:260-263.
  * gemm_path selects the tcgen05 or the CUDA-core kernel. */
-int arcb_op_gemm(const void* d_a16, const void* d_w_bf16, float* d_y, int32_t M, int32_t N,
+int arcb_op_gemm(const void* d_a16, const void* d_w16, float* d_y, int32_t M, int32_t N,
                  int32_t K, int32_t act_format, int32_t gemm_path, void* stream);
 
 /* Attention of one query vector per item over a cached K/V prefix:

@@ -42,14 +42,16 @@ static int fail_cuda(cudaError_t e, const char* where) {
     }                                                              \
   } while (0)
 
+// GEMM weights hold the bf16-rounded parameter values in the 16-bit container of the activations
+// (half or bfloat16), because the tensor-core MMA needs both operands in one format.
 struct LayerWeights {
   float* ln1_w = nullptr;
-  __nv_bfloat16* w_qkv = nullptr;   // [3d][d]
-  __nv_bfloat16* w_out = nullptr;   // [d][d]
+  uint16_t* w_qkv = nullptr;   // [3d][d]
+  uint16_t* w_out = nullptr;   // [d][d]
   float* ln2_w = nullptr;
-  __nv_bfloat16* w_gu = nullptr;    // [2 dff][d], 64 gate rows then the matching 64 up rows, repeated
-  float* b_gu = nullptr;            // [2 dff] packed the same way
-  __nv_bfloat16* w_down = nullptr;  // [d][dff]
+  uint16_t* w_gu = nullptr;    // [2 dff][d], 64 gate rows then the matching 64 up rows, repeated
+  float* b_gu = nullptr;       // [2 dff] packed the same way
+  uint16_t* w_down = nullptr;  // [d][dff]
   float* b_down = nullptr;          // [d]
 };
 
@@ -78,6 +80,8 @@ struct arcb_session {
   uint16_t* q16 = nullptr;
   uint16_t* attn16 = nullptr;
   uint16_t* h16 = nullptr;
+  uint16_t* k16 = nullptr;  // K/V of one prefill call in the activation format
+  uint16_t* v16 = nullptr;
   float* attn_scratch = nullptr;
   int* example_ids = nullptr;
   bool use_examples = false;
@@ -129,6 +133,7 @@ extern "C" int arcb_engine_create(const arcb_config* cfg, arcb_engine** out) {
     return fail(ARCB_E_ARG, "bad table extents");
   if (!arcb_device_ok()) return fail(ARCB_E_UNSUPPORTED, "current device is not compute capability 10.x");
   CKL(arcb_gemm_init(), "gemm init (shared-memory opt-in / cuTensorMapEncodeTiled lookup)");
+  CKL(arcb_attn_prefill_init(), "prefill attention init (shared-memory opt-in)");
   arcb_engine* e = new arcb_engine();
   e->cfg = *cfg;
   cudaGetDevice(&e->device);
@@ -214,6 +219,7 @@ extern "C" int arcb_engine_load_tensor(arcb_engine* e, int32_t kind, int32_t lay
     CK(cudaMemcpyAsync(dst, src, (size_t)numel * sizeof(float), cudaMemcpyDeviceToDevice, stream));
   } else {
     if (blk == 0) { blk = (int)rows; blk_stride = (int)rows; }
+    if (to_bf16 && e->act_f16()) to_bf16 = 2;
     CKL(arcb_launch_pack_rows(src, dst, rows, cols, blk, blk_stride, blk_off, to_bf16, stream), "pack_rows");
   }
   e->loaded[(size_t)kind * c.n_layers + (per_layer ? layer : 0)] = 1;
@@ -244,7 +250,7 @@ static int choose_splits(const arcb_engine* e, int n_seqs, int requested) {
 }
 
 struct WsLayout {
-  size_t x, xn, q, attn, h, scratch, ints, total;
+  size_t x, xn, q, attn, h, k16, v16, scratch, ints, total;
   size_t n_int;
 };
 
@@ -258,6 +264,8 @@ static WsLayout ws_layout(const arcb_engine* e, int B, int P, int splits) {
   w.q = off; off = align_up(off + R * d * 2, 256);
   w.attn = off; off = align_up(off + R * d * 2, 256);
   w.h = off; off = align_up(off + R * dff * 2, 256);
+  w.k16 = off; off = align_up(off + (size_t)P * d * 2, 1024);
+  w.v16 = off; off = align_up(off + (size_t)P * d * 2, 1024);
   w.scratch = off;
   off = align_up(off + (splits > 1 ? (size_t)B * e->cfg.n_heads * splits * ATTN_SCRATCH_STRIDE * 4 : 0), 256);
   w.ints = off;
@@ -302,6 +310,8 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
   s->q16 = reinterpret_cast<uint16_t*>(base + w.q);
   s->attn16 = reinterpret_cast<uint16_t*>(base + w.attn);
   s->h16 = reinterpret_cast<uint16_t*>(base + w.h);
+  s->k16 = reinterpret_cast<uint16_t*>(base + w.k16);
+  s->v16 = reinterpret_cast<uint16_t*>(base + w.v16);
   s->attn_scratch = splits > 1 ? reinterpret_cast<float*>(base + w.scratch) : nullptr;
   int* ints = reinterpret_cast<int*>(base + w.ints);
   const int B = dsc->n_seqs;
@@ -363,15 +373,20 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
   ep.pos = pos; ep.slot = slot; ep.seq = seq; ep.kcache = kbase; ep.vcache = vbase;
   ep.t_max = T; ep.n_heads = c.n_heads; ep.d_model = d; ep.n_seqs = B;
   ep.rope = e->rope; ep.max_x = c.max_x; ep.max_y = c.max_y; ep.max_z = c.max_z;
+  const bool want_flash = prefill && c.attn_path == ARCB_ATTN_AUTO && pa && pa->n_qblocks > 0 && pa->d_kv_row &&
+                          pa->d_qblock_kv0 && pa->n_kv_rows > 0 && arcb_attn_prefill_available();
+  if (want_flash) { ep.k16 = s->k16; ep.v16 = s->v16; ep.kv_row = pa->d_kv_row; }
   CKL(arcb_launch_gemm(s->xn16, L.w_qkv, ep, d, f16, use_tc_for(e, rows, 3 * d, d), stream), "qkv gemm");
 
   // attention
-  bool flash = prefill && c.attn_path == ARCB_ATTN_AUTO && pa && pa->n_qblocks > 0 && arcb_attn_prefill_available();
+  const bool flash = prefill && c.attn_path == ARCB_ATTN_AUTO && pa && pa->n_qblocks > 0 && pa->d_kv_row &&
+                     pa->d_qblock_kv0 && pa->n_kv_rows > 0 && arcb_attn_prefill_available();
   if (flash) {
     AttnPrefillArgs fa{};
-    fa.q16 = s->q16; fa.k = kbase; fa.v = vbase; fa.out16 = s->attn16;
+    fa.q16 = s->q16; fa.k16 = s->k16; fa.v16 = s->v16; fa.out16 = s->attn16;
     fa.seq = seq; fa.kv_count = kv_count; fa.qblock_row0 = pa->d_qblock_row0; fa.qblock_rows = pa->d_qblock_rows;
-    fa.n_qblocks = pa->n_qblocks; fa.n_rows = rows; fa.n_heads = c.n_heads; fa.t_max = T; fa.n_seqs = B;
+    fa.qblock_kv0 = pa->d_qblock_kv0;
+    fa.n_qblocks = pa->n_qblocks; fa.n_rows = rows; fa.n_kv_rows = pa->n_kv_rows; fa.n_heads = c.n_heads;
     fa.act_f16 = f16; fa.err = e->d_err;
     CKL(arcb_launch_attn_prefill(fa, stream), "prefill attention");
   } else {
@@ -404,6 +419,8 @@ extern "C" int arcb_prefill(arcb_session* s, const arcb_prefill_args* a, void* s
   if (!s || !a) return fail(ARCB_E_ARG, "null argument");
   if (a->n_tokens <= 0 || a->n_tokens > s->desc.max_prefill_tokens)
     return fail(ARCB_E_ARG, "n_tokens outside (0, max_prefill_tokens]");
+  if (a->n_kv_rows < 0 || a->n_kv_rows > s->desc.max_prefill_tokens)
+    return fail(ARCB_E_ARG, "n_kv_rows outside [0, max_prefill_tokens]");
   if (!a->d_token_ids || !a->d_pos_xyz || !a->d_seq || !a->d_kv_slot || !a->d_kv_count)
     return fail(ARCB_E_ARG, "null token arrays");
   if (a->n_first < 0 || (a->n_first > 0 && (!a->d_first_row || !a->d_first_seq || !a->d_prompt_len ||

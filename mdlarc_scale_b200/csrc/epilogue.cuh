@@ -25,6 +25,9 @@ struct GemmEpilogue {
   const int* seq;   // [M] cache row (sequence) of the token; null = row index
   __nv_bfloat16* kcache;  // layer K base [B][H][t_max][64]
   __nv_bfloat16* vcache;  // layer V base
+  void* k16;              // optional [n_kv_rows][d]: K of this call in the activation format
+  void* v16;              //   (operands of the tensor-core prefill attention)
+  const int* kv_row;      // [M] row of k16/v16 for this token, < 0: none
   int t_max, n_heads, d_model, n_seqs;
   const float* rope;  // cos_x | sin_x | cos_y | sin_y | cos_z | sin_z
   int max_x, max_y, max_z;
@@ -34,10 +37,12 @@ struct GemmEpilogue {
 struct RopeRow {
   int x, y, z;
   long long kv_row;  // (seq * H) * t_max + slot, or -1
+  int row16;         // row of k16/v16, or -1
 };
 
 __device__ __forceinline__ RopeRow rope_row_ctx(const GemmEpilogue& e, int m) {
   RopeRow r;
+  r.row16 = (e.k16 && e.kv_row) ? e.kv_row[m] : -1;
   const int px = e.pos[3 * m + 0], py = e.pos[3 * m + 1], pz = e.pos[3 * m + 2];
   r.x = min(max(px, 0), e.max_x - 1);
   r.y = min(max(py, 0), e.max_y - 1);
@@ -94,13 +99,22 @@ __device__ __forceinline__ void epi_qkv_quad(const GemmEpilogue& e, const RopeRo
     pk.x = pack2_act(v.x, v.y, e.act_f16);
     pk.y = pack2_act(v.z, v.w, e.act_f16);
     *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(e.out16) + (size_t)m * d + c) = pk;
-  } else if (r.kv_row >= 0) {
-    __nv_bfloat16* base = (sec == 1) ? e.kcache : e.vcache;
-    const long long row = r.kv_row + (long long)h * e.t_max;
-    uint2 pk;
-    pk.x = pack2_bf16(v.x, v.y);
-    pk.y = pack2_bf16(v.z, v.w);
-    *reinterpret_cast<uint2*>(base + row * ARCB_HEAD_DIM + dim) = pk;
+  } else {
+    if (r.kv_row >= 0) {
+      __nv_bfloat16* base = (sec == 1) ? e.kcache : e.vcache;
+      const long long row = r.kv_row + (long long)h * e.t_max;
+      uint2 pk;
+      pk.x = pack2_bf16(v.x, v.y);
+      pk.y = pack2_bf16(v.z, v.w);
+      *reinterpret_cast<uint2*>(base + row * ARCB_HEAD_DIM + dim) = pk;
+    }
+    if (r.row16 >= 0) {
+      uint16_t* base16 = reinterpret_cast<uint16_t*>((sec == 1) ? e.k16 : e.v16);
+      uint2 pk;
+      pk.x = pack2_act(v.x, v.y, e.act_f16);
+      pk.y = pack2_act(v.z, v.w, e.act_f16);
+      *reinterpret_cast<uint2*>(base16 + (size_t)r.row16 * d + c) = pk;
+    }
   }
 }
 

@@ -1,4 +1,5 @@
-// y = A[M,K] (16-bit activations) * W[N,K]^T (bf16 weights), fp32 accumulate, with the
+// y = A[M,K] * W[N,K]^T, both operands in the same 16-bit format (half or bfloat16: tcgen05
+// kind::f16 rejects mixed A/B formats with an illegal-instruction fault), fp32 accumulate, with the
 // fused epilogues of epilogue.cuh.  Two kernels:
 //   gemm_tc_kernel   : tcgen05.mma (UMMA 128xBNx16, accumulator in TMEM), operands
 //                      staged by TMA (128-byte swizzle) through an mbarrier ring;
@@ -131,6 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       RopeRow rr;
       rr.x = rr.y = rr.z = 0;
       rr.kv_row = -1;
+      rr.row16 = -1;
       if (MODE == EPI_QKV_ROPE && row_ok) rr = rope_row_ctx(ep, m);
       if constexpr (MODE == EPI_SWIGLU) {
         // gate columns [0,64) and up columns [64,128) of every 128-column group
@@ -225,7 +227,7 @@ gemm_simt_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ W,
       const uint32_t w[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const float2 f = unpack2_bf16(w[j]);
+        const float2 f = unpack2_act(w[j], a_f16);
         Ws[w_kh + 2 * j][w_n] = f.x;
         Ws[w_kh + 2 * j + 1][w_n] = f.y;
       }
@@ -326,7 +328,7 @@ int arcb_gemm_init() {
 }
 
 template <int MODE>
-static int launch_gemm_mode(const void* a16, const void* w_bf16, const GemmEpilogue& ep, int K,
+static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue& ep, int K,
                             int act_f16, bool use_tc, cudaStream_t stream) {
   const int M = ep.M, N = ep.N;
   if (use_tc) {
@@ -334,32 +336,32 @@ static int launch_gemm_mode(const void* a16, const void* w_bf16, const GemmEpilo
     CUtensorMap ta, tb;
     int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
     if (r) return 1000 + r;
-    r = arcb_make_tmap_2d_16b(&tb, w_bf16, (uint64_t)N, (uint64_t)K, BN, TC_BK, 0);
+    r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, BN, TC_BK, act_f16);
     if (r) return 1000 + r;
-    const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, 1);
+    const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
     dim3 grid(N / BN, (M + TC_BM - 1) / TC_BM);
     gemm_tc_kernel<BN, MODE><<<grid, 192, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc);
   } else {
     dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
     gemm_simt_kernel<MODE><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a16),
-                                                     reinterpret_cast<const uint16_t*>(w_bf16), ep, K,
+                                                     reinterpret_cast<const uint16_t*>(w16), ep, K,
                                                      act_f16);
   }
   arcb_count_launch(1);
   return (int)cudaGetLastError();
 }
 
-int arcb_launch_gemm(const void* a16, const void* w_bf16, const GemmEpilogue& ep, int K, int act_f16,
+int arcb_launch_gemm(const void* a16, const void* w16, const GemmEpilogue& ep, int K, int act_f16,
                      bool use_tc, cudaStream_t stream) {
   const int M = ep.M, N = ep.N;
   if (M <= 0) return 0;
   if (N % 128 != 0 || K % 32 != 0) return -1;
   if (use_tc && !arcb_gemm_tc_supported(M, N, K)) return -1;
   switch (ep.mode) {
-    case EPI_STORE_F32: return launch_gemm_mode<EPI_STORE_F32>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
-    case EPI_QKV_ROPE: return launch_gemm_mode<EPI_QKV_ROPE>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
-    case EPI_RESID: return launch_gemm_mode<EPI_RESID>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
-    case EPI_SWIGLU: return launch_gemm_mode<EPI_SWIGLU>(a16, w_bf16, ep, K, act_f16, use_tc, stream);
+    case EPI_STORE_F32: return launch_gemm_mode<EPI_STORE_F32>(a16, w16, ep, K, act_f16, use_tc, stream);
+    case EPI_QKV_ROPE: return launch_gemm_mode<EPI_QKV_ROPE>(a16, w16, ep, K, act_f16, use_tc, stream);
+    case EPI_RESID: return launch_gemm_mode<EPI_RESID>(a16, w16, ep, K, act_f16, use_tc, stream);
+    case EPI_SWIGLU: return launch_gemm_mode<EPI_SWIGLU>(a16, w16, ep, K, act_f16, use_tc, stream);
   }
   return -1;
 }

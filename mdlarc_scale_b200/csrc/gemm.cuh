@@ -3,10 +3,10 @@
 #include <cuda.h>
 #include "epilogue.cuh"
 
-// A: [M][K] 16-bit activations (half when act_f16, else bfloat16); W: [N][K] bfloat16.
+// A: [M][K] and W: [N][K], both half when act_f16, else both bfloat16.
 // Requires N % 128 == 0; the tcgen05 path also K % 64 == 0, the CUDA-core path K % 32 == 0.
 // Returns 0, a negative argument error, a cudaError_t, or 1000 + CUresult of the tensor-map encode.
-int arcb_launch_gemm(const void* a16, const void* w_bf16, const GemmEpilogue& ep, int K, int act_f16,
+int arcb_launch_gemm(const void* a16, const void* w16, const GemmEpilogue& ep, int K, int act_f16,
                      bool use_tc, cudaStream_t stream);
 int arcb_gemm_init();
 bool arcb_gemm_tc_supported(int M, int N, int K);

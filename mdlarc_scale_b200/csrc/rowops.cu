@@ -201,8 +201,9 @@ head_kernel(HeadArgs a, DecodeState st) {
   st.cur_tok[b] = tok;
 }
 
-// dst row = (r / blk) * blk_stride + blk_off + r % blk ; to_bf16: store bf16, else fp32 holding
-// the bf16-rounded value.
+// dst row = (r / blk) * blk_stride + blk_off + r % blk.  Every value is first rounded to bf16 (the
+// model's precision); container: 0 = fp32, 1 = bf16, 2 = IEEE half holding the bf16-rounded value
+// (exact for |w| >= 2^-14, within 2^-25 absolute below; saturates at +-65504).
 __global__ void pack_rows_kernel(const float* __restrict__ src, void* __restrict__ dst, long long rows,
                                  long long cols, int blk, int blk_stride, int blk_off, int to_bf16) {
   const long long n = rows * cols;
@@ -211,8 +212,14 @@ __global__ void pack_rows_kernel(const float* __restrict__ src, void* __restrict
     const long long r = i / cols, c = i - r * cols;
     const long long dr = (r / blk) * blk_stride + blk_off + (r % blk);
     const __nv_bfloat16 h = __float2bfloat16_rn(src[i]);
-    if (to_bf16) reinterpret_cast<__nv_bfloat16*>(dst)[dr * cols + c] = h;
-    else reinterpret_cast<float*>(dst)[dr * cols + c] = __bfloat162float(h);
+    if (to_bf16 == 1) {
+      reinterpret_cast<__nv_bfloat16*>(dst)[dr * cols + c] = h;
+    } else if (to_bf16 == 2) {
+      const float f = fminf(fmaxf(__bfloat162float(h), -65504.f), 65504.f);
+      reinterpret_cast<__half*>(dst)[dr * cols + c] = __float2half_rn(f);
+    } else {
+      reinterpret_cast<float*>(dst)[dr * cols + c] = __bfloat162float(h);
+    }
   }
 }
 

@@ -225,6 +225,7 @@ class Session:
             d_seq=_ptr(plan.seq), d_kv_slot=_ptr(plan.kv_slot), d_kv_count=_ptr(plan.kv_count),
             d_example_ids=_ptr(example_ids),
             n_qblocks=plan.n_qblocks, d_qblock_row0=_ptr(plan.qblock_row0), d_qblock_rows=_ptr(plan.qblock_rows),
+            d_qblock_kv0=_ptr(plan.qblock_kv0), d_kv_row=_ptr(plan.kv_row), n_kv_rows=plan.n_kv_rows,
             d_logits_all=_ptr(logits_all),
             n_first=plan.n_first, d_first_row=_ptr(plan.first_row), d_first_seq=_ptr(plan.first_seq),
             d_prompt_len=_ptr(plan.prompt_len), d_grid_x=_ptr(plan.grid_x), d_grid_y=_ptr(plan.grid_y),
@@ -259,6 +260,9 @@ class PrefillPlan:
     n_qblocks: int
     qblock_row0: torch.Tensor | None
     qblock_rows: torch.Tensor | None
+    qblock_kv0: torch.Tensor | None = None   # first K/V scratch row of each block's sequence
+    kv_row: torch.Tensor | None = None       # K/V scratch row of each token (-1: query-only)
+    n_kv_rows: int = 0
     n_first: int = 0
     first_row: torch.Tensor | None = None
     first_seq: torch.Tensor | None = None
@@ -272,13 +276,14 @@ class PrefillPlan:
             return None if t is None else t.to(device, non_blocking=True)
         return PrefillPlan(self.n_tokens, mv(self.token_ids), mv(self.pos_xyz), mv(self.seq), mv(self.kv_slot),
                            mv(self.kv_count), self.n_qblocks, mv(self.qblock_row0), mv(self.qblock_rows),
+                           mv(self.qblock_kv0), mv(self.kv_row), self.n_kv_rows,
                            self.n_first, mv(self.first_row), mv(self.first_seq), mv(self.prompt_len),
                            mv(self.grid_x), mv(self.grid_y), mv(self.grid_in_output))
 
     def h2d_bytes(self) -> int:
         n = 0
         for t in (self.token_ids, self.pos_xyz, self.seq, self.kv_slot, self.kv_count, self.qblock_row0,
-                  self.qblock_rows, self.first_row, self.first_seq, self.prompt_len, self.grid_x, self.grid_y,
+                  self.qblock_rows, self.qblock_kv0, self.kv_row, self.first_row, self.first_seq, self.prompt_len, self.grid_x, self.grid_y,
                   self.grid_in_output):
             if t is not None:
                 n += t.numel() * t.element_size()
@@ -385,10 +390,16 @@ def plan_prefill(ids: np.ndarray, pos: np.ndarray, mask: np.ndarray, rows: np.nd
             prompt_len=torch.from_numpy(lens.astype(np.int32)),
             grid_x=torch.from_numpy(gx), grid_y=torch.from_numpy(gy), grid_in_output=torch.from_numpy(gin))
     qb0, qbn = _qblocks(seq)
+    # K/V scratch of the call: the valid keys of sequence i occupy rows [kv_base[i], kv_base[i] + len_i)
+    kv_base = np.concatenate([[0], np.cumsum(lens)[:-1]]).astype(np.int64)
+    local = np.searchsorted(rows, seq)  # index of each token's sequence within this call (rows is sorted)
+    kv_row = np.where(slot >= 0, kv_base[local] + slot, -1).astype(np.int32)
+    qb_kv0 = kv_base[local[qb0]].astype(np.int32) if len(qb0) else np.zeros(0, np.int32)
     return PrefillPlan(
         n_tokens=len(tok), token_ids=torch.from_numpy(tok), pos_xyz=torch.from_numpy(np.ascontiguousarray(pxyz)),
         seq=torch.from_numpy(seq), kv_slot=torch.from_numpy(slot), kv_count=torch.from_numpy(cnt),
         n_qblocks=len(qb0), qblock_row0=torch.from_numpy(qb0), qblock_rows=torch.from_numpy(qbn),
+        qblock_kv0=torch.from_numpy(qb_kv0), kv_row=torch.from_numpy(kv_row), n_kv_rows=int(lens.sum()),
         n_first=n_first, **plan_first)
 
 

@@ -37,7 +37,7 @@ def test_struct_sizes_match_c_layout():
     from mdlarc_scale_b200 import _lib
     assert C.sizeof(_lib.Config) == 14 * 4
     assert C.sizeof(_lib.SessionDesc) == 6 * 4 + 7 * 8
-    assert C.sizeof(_lib.PrefillArgs) == 152
+    assert C.sizeof(_lib.PrefillArgs) == 176
 
 
 def test_argument_errors_without_gpu(lib):

@@ -1,0 +1,148 @@
+"""The CUDA path (through the public API -> C ABI) against the CPU oracle and the committed
+reference outputs.  Tolerance: logits within 2e-2 max-abs of the fp32 forward on the same
+bf16-rounded weights; greedy tokens identical except where the reference's own top-2 logit
+margin is below that tolerance."""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import first_end_trim, have_b200, tokens_agree
+from oracle import arc_model as om
+from oracle import arc_tokens as ot
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+# kernel selections: CUDA-core GEMM + streaming attention (cross-check), tcgen05 GEMM + streaming
+# prefill attention, and the production path (tcgen05 GEMM + tcgen05 flash prefill)
+PATHS = {"simt-stream": ("simt", "stream"), "tc-stream": ("auto", "stream"), "tc-flash": ("auto", "auto")}
+
+
+def _weights(name, size="tiny"):
+    cfg = om.make_config(size, max_seq_len=4096)
+    kw = dict(embed_gain=8.0) if name == "varied" else {}
+    return cfg, om.round_bf16(om.perturb_state(om.init_state(cfg, seed=0, **kw), seed=1))
+
+
+@pytest.fixture(scope="module")
+def engines():
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+    from mdlarc_scale_b200.engine import Engine
+    out = {}
+    for name in ("plain", "varied"):
+        cfg, sd = _weights(name)
+        for path, (gemm, attn) in PATHS.items():
+            out[name, path] = (Engine(sd, cfg, "cuda:0", gemm_path=gemm, attn_path=attn), cfg, sd)
+    return out
+
+
+@pytest.mark.parametrize("path", list(PATHS))
+@pytest.mark.parametrize("name", ["plain", "varied"])
+@pytest.mark.parametrize("pad", ["right", "left"])
+def test_forward_logits_vs_reference(engines, golden_model, name, pad, path):
+    from mdlarc_scale_b200.transformer import forward_logits
+    eng, cfg, sd = engines[name, path]
+    k = f"{name}_{pad}"
+    ids, pos = torch.from_numpy(golden_model[k + "_ids"]), torch.from_numpy(golden_model[k + "_pos"])
+    ex, mask = torch.from_numpy(golden_model[k + "_ex"]), torch.from_numpy(golden_model[k + "_mask"])
+    got = forward_logits(eng, ids, pos, ex, mask).cpu()
+    want = torch.from_numpy(golden_model[k + "_logits"])  # the reference's own fp32 forward
+    err = (got[mask] - want[mask]).abs().max().item()
+    assert err < TOL, f"max abs logit error {err}"
+    got = forward_logits(eng, torch.from_numpy(golden_model[f"{name}_nomask_ids"]),
+                         torch.from_numpy(golden_model[f"{name}_nomask_pos"])).cpu()
+    err = (got - torch.from_numpy(golden_model[f"{name}_nomask_logits"])).abs().max().item()
+    assert err < TOL, f"max abs logit error {err} (no mask, no example ids)"
+
+
+@pytest.mark.parametrize("path", list(PATHS))
+@pytest.mark.parametrize("name", ["plain", "varied"])
+@pytest.mark.parametrize("pad", ["right", "left"])
+def test_generate_vs_reference_tokens(engines, golden_model, name, pad, path):
+    from mdlarc_scale_b200.inference import generate_output
+    eng, cfg, sd = engines[name, path]
+    k = f"{name}_{pad}"
+    ids, pos = torch.from_numpy(golden_model[k + "_ids"]), torch.from_numpy(golden_model[k + "_pos"])
+    ex, mask = torch.from_numpy(golden_model[k + "_ex"]), torch.from_numpy(golden_model[k + "_mask"])
+    S = ids.shape[1]
+    for stop, key, n_new in ((True, "_gen", 48), (False, "_gen_nostop", 24)):
+        got = generate_output(eng, ids, pos, ex, mask, max_new_tokens=n_new, stop_on_end=stop)
+        want = golden_model[k + key]
+        assert got.dtype == torch.int64 and torch.equal(got[:, :S], ids)
+        if stop:
+            assert got.shape[1] == want.shape[1]  # same stopping step as the reference
+        ref = om.generate(sd, cfg, ids, pos, ex, mask, max_new_tokens=n_new, stop_on_end=stop, keep_logits=True)
+        for b in range(ids.shape[0]):
+            g = got[b, S:].tolist()
+            w = want[b, S:].tolist()
+            if stop:  # rows agree through their first END (frozen afterwards here)
+                g, w = first_end_trim(g), first_end_trim(w)
+            ok, where = tokens_agree(g, w, [lg[b].numpy() for lg in ref.logits], TOL)
+            assert ok, f"row {b} diverges at generated index {where} with a clear reference margin"
+
+
+@pytest.mark.parametrize("path", list(PATHS))
+def test_teacher_forced_step_logits(engines, path):
+    """Every decode step's logits against the oracle's full-sequence forward, on a well-formed
+    continuation (colours, NEWLINEs, END) so that all grid-state transitions are exercised."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    eng, cfg, sd = engines["varied", path]
+    tasks = synthetic.capped_tasks(21, 3, 1, 2, 2, 9, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    rng = np.random.default_rng(4)
+    conts = []
+    for _ in prompts:
+        g = synthetic.random_grid(rng, 2, 6)
+        conts.append(ot.grid_to_tokens(g) + [13])
+    n_new = max(len(c) for c in conts)
+    forced = np.full((len(prompts), n_new), 13, dtype=np.int32)
+    for i, c in enumerate(conts):
+        forced[i, :len(c)] = c
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ex = np.array([1, 2, 3])
+    tr = generate_tokens(eng, ids, pos, mask, ex, n_new, stop_on_end=False, forced=forced, want_logits=True)
+    assert torch.equal(tr.tokens.cpu(), torch.from_numpy(forced))
+    step_logits = tr.step_logits.cpu()
+    worst = 0.0
+    for b, p in enumerate(prompts):
+        full = p + forced[b].tolist()
+        fpos = torch.from_numpy(ot.positions_3d(full))[None]
+        ref = om.forward(sd, cfg, torch.tensor([full]), fpos, torch.tensor([ex[b]]))[0]
+        # logits that predict generated token i come from position len(p)-1+i
+        want = ref[len(p) - 1: len(p) - 1 + n_new]
+        worst = max(worst, (step_logits[b] - want).abs().max().item())
+    assert worst < TOL, f"max abs decode-step logit error {worst}"
+
+
+def test_greedy_is_deterministic_and_split_invariant(engines):
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    eng, cfg, sd = engines["varied", "tc-flash"]
+    tasks = synthetic.capped_tasks(31, 6, 1, 2, 2, 8, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    a = generate_tokens(eng, ids, pos, mask, None, 40, stop_on_end=False, attn_splits=1).tokens.cpu()
+    b = generate_tokens(eng, ids, pos, mask, None, 40, stop_on_end=False, attn_splits=1).tokens.cpu()
+    assert torch.equal(a, b)  # bitwise repeatable (tests/test_inference.py:82-98 asserts the same)
+    c = generate_tokens(eng, ids, pos, mask, None, 40, stop_on_end=False, attn_splits=5, want_logits=True)
+    d = generate_tokens(eng, ids, pos, mask, None, 40, stop_on_end=False, attn_splits=1, want_logits=True)
+    # split-K only re-associates the softmax sums: logits agree to fp32 round-off level
+    assert (c.step_logits[:, :8] - d.step_logits[:, :8]).abs().max().item() < 5e-3
+
+
+def test_predict_with_augmentations_and_vote(engines):
+    import random
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import predict_with_augmentations
+    from mdlarc_scale_b200.voting import aaivr_predict
+    from oracle import arc_vote
+    eng, cfg, sd = engines["varied", "tc-flash"]
+    task = synthetic.capped_tasks(41, 1, 2, 2, 2, 5, None)[0]
+    preds = predict_with_augmentations(eng, task, 0, "cuda:0", num_color_perms=3, max_output_tokens=24)
+    assert len(preds) == 8 * 3                       # tests/test_inference.py:225-241
+    assert preds[0][1] == 0 and preds[0][2] is None  # tests/test_inference.py:263-278
+    assert sorted({d for _, d, _ in preds}) == list(range(8))
+    mine = aaivr_predict(preds, 2, task["test"][0]["input"], rng=random.Random(5))
+    ref = arc_vote.aaivr_predict(preds, 2, task["test"][0]["input"], rng=random.Random(5))
+    assert mine == ref  # votes bit-exact given identical candidates
