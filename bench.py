@@ -256,6 +256,11 @@ def run_ours(args, rank, world, local_rank):
     session.close()
     del session
     torch.cuda.empty_cache()
+    if args.no_e2e:
+        if rank == 0:
+            print(json.dumps({"profiling_run": True, "value": world * args.steps * B * MAX_NEW / dt,
+                              "attn_gbs": attn_gbs, "prefill_tok_s": prefill_tok_s, "gpu_launches": launches}))
+        return
     host = []
     for ids, pos, mask in batches:
         host.append((torch.from_numpy(ids).pin_memory(), torch.from_numpy(pos).pin_memory(),
@@ -325,6 +330,7 @@ def run_ours(args, rank, world, local_rank):
 
 
 def main():
+    global MAX_NEW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
@@ -334,7 +340,11 @@ def main():
     ap.add_argument("--cpu-seqs", type=int, default=16)
     ap.add_argument("--cpu-steps", type=int, default=48)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--max-new", type=int, default=MAX_NEW,
+                    help="tokens generated per sequence (the workload uses 931; smaller only for profiling)")
     args = ap.parse_args()
+    MAX_NEW = args.max_new
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))

@@ -145,9 +145,9 @@ class Engine:
 
     def new_session(self, n_seqs: int, t_max: int, max_new: int, max_prefill_tokens: int,
                     stop_on_end: bool = True, attn_splits: int = 0, forced: torch.Tensor | None = None,
-                    want_step_logits: bool = False) -> "Session":
+                    want_step_logits: bool = False, out_tokens: torch.Tensor | None = None) -> "Session":
         return Session(self, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end, attn_splits,
-                       forced, want_step_logits)
+                       forced, want_step_logits, out_tokens)
 
 
 _ENGINES: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
@@ -173,7 +173,7 @@ class Session:
     """A static KV cache, the greedy-loop state and the decode graph for ``n_seqs`` sequences."""
 
     def __init__(self, eng: Engine, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end,
-                 attn_splits, forced, want_step_logits):
+                 attn_splits, forced, want_step_logits, out_tokens=None):
         self.eng = eng
         self.n_seqs, self.t_max, self.max_new = int(n_seqs), int(t_max), int(max_new)
         self.max_prefill_tokens = int(max_prefill_tokens)
@@ -187,7 +187,12 @@ class Session:
         # torch owns the memory; the library only borrows the pointers
         self.kv_cache = torch.empty(kv_bytes, dtype=torch.uint8, device=dev)
         self.workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
-        self.out_tokens = torch.full((self.n_seqs, self.max_new), END_TOKEN_ID, dtype=torch.int32, device=dev)
+        if out_tokens is None:
+            out_tokens = torch.full((self.n_seqs, self.max_new), END_TOKEN_ID, dtype=torch.int32, device=dev)
+        elif (out_tokens.dtype != torch.int32 or tuple(out_tokens.shape) != (self.n_seqs, self.max_new)
+              or not out_tokens.is_contiguous() or out_tokens.device != dev):
+            raise ValueError("out_tokens must be a contiguous int32 [n_seqs, max_new] tensor on the engine's device")
+        self.out_tokens = out_tokens  # may be a slice of a caller-owned (e.g. all-gather) buffer
         self.forced = None
         if forced is not None:
             self.forced = forced.to(device=dev, dtype=torch.int32).contiguous()
