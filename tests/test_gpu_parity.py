@@ -146,3 +146,41 @@ def test_predict_with_augmentations_and_vote(engines):
     mine = aaivr_predict(preds, 2, task["test"][0]["input"], rng=random.Random(5))
     ref = arc_vote.aaivr_predict(preds, 2, task["test"][0]["input"], rng=random.Random(5))
     assert mine == ref  # votes bit-exact given identical candidates
+
+
+def test_large_model_logits_within_tolerance():
+    """The benchmark model (large: d 1280, 20 heads, 12 layers, d_ff 3392), production kernels:
+    all prompt positions and 12 teacher-forced decode steps against the fp32 oracle forward on the
+    same bf16-rounded weights."""
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    from mdlarc_scale_b200.transformer import forward_logits
+    torch.set_num_threads(max(1, (torch.get_num_threads())))
+    cfg = om.make_config("large", max_seq_len=4096)
+    sd = om.round_bf16(om.init_state(cfg, seed=0))
+    eng = Engine(sd, cfg, "cuda:0")
+    tasks = synthetic.capped_tasks(51, 2, 2, 2, 3, 10, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
+    ex = torch.tensor([5, 9])
+    got = forward_logits(eng, ids_t, pos_t, ex, mask_t).cpu()
+    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
+    err = (got[mask_t] - want[mask_t]).abs().max().item()
+    assert err < TOL, f"large model: max abs prompt-logit error {err}"
+    n_new = 12
+    rng = np.random.default_rng(0)
+    forced = rng.integers(0, 10, size=(2, n_new)).astype(np.int32)
+    forced[:, 5] = 11
+    tr = generate_tokens(eng, ids, pos, mask, ex.numpy(), n_new, stop_on_end=False, forced=forced, want_logits=True)
+    worst = 0.0
+    for b, p in enumerate(prompts):
+        full = p + forced[b].tolist()
+        fpos = torch.from_numpy(ot.positions_3d(full))[None]
+        ref = om.forward(sd, cfg, torch.tensor([full]), fpos, ex[b:b + 1])[0]
+        worst = max(worst, (tr.step_logits[b].cpu() - ref[len(p) - 1: len(p) - 1 + n_new]).abs().max().item())
+    assert worst < TOL, f"large model: max abs decode-step logit error {worst}"
+    eng.close()
