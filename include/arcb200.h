@@ -213,6 +213,26 @@ int arcb_op_decode_attention(const void* d_q16, const void* d_k, const void* d_v
                              int32_t t_max, int32_t n_splits, void* d_scratch, int32_t act_format,
                              void* stream);
 
+/* Same operation as arcb_op_decode_attention for callers that cannot allocate device memory
+ * (a serving loop with a fixed memory pool, a plugin living inside another framework's allocator,
+ * code inside a region where cudaMalloc/cudaFree and their implicit synchronisation are
+ * forbidden).  It has no counterpart in the reference, which never leaves PyTorch's allocator.
+ * The per-split partial results live in an array built into the library instead of a caller
+ * buffer, so there is no d_scratch argument and the call makes no allocation of any kind.
+ *   - limit: n_items * n_heads * n_splits <= ARCB_STATIC_ATTN_MAX_RECORDS (4.25 MiB of scratch,
+ *     held by every GPU that loads the library until the process exits); larger requests return
+ *     ARCB_E_ARG with a message;
+ *   - the first call on a device resolves the array's address on that device; make that first
+ *     call before any CUDA stream capture;
+ *   - all calls on a device share the array, which keeps the last call's contents (nothing in
+ *     it needs to start at zero); calls that overlap on the GPU race, so keep them on one stream
+ *     or otherwise ordered. */
+#define ARCB_STATIC_ATTN_MAX_RECORDS 16384
+int arcb_op_decode_attention_static(const void* d_q16, const void* d_k, const void* d_v, void* d_out16,
+                                    const int32_t* d_item_seq, const int32_t* d_item_len,
+                                    const uint8_t* d_item_skip, int32_t n_items, int32_t n_heads,
+                                    int32_t t_max, int32_t n_splits, int32_t act_format, void* stream);
+
 /* ln_f -> lm_head -> argmax (src/inference.py:418/424/459 + 574/611): logits fp32
  * [rows][14] and the index of the first maximum. d_row_index (optional) gathers rows of x. */
 int arcb_op_head(const float* d_x, const int32_t* d_row_index, const float* d_lnf_w,

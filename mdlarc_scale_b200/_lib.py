@@ -27,8 +27,10 @@ EXPORTS = [
     "arcb_engine_load_tensor", "arcb_session_workspace_bytes", "arcb_kv_cache_bytes",
     "arcb_session_create", "arcb_session_destroy", "arcb_prefill", "arcb_decode",
     "arcb_session_poll", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
-    "arcb_attn_scratch_bytes", "arcb_op_decode_attention", "arcb_op_head",
+    "arcb_attn_scratch_bytes", "arcb_op_decode_attention", "arcb_op_decode_attention_static",
+    "arcb_op_head",
 ]
+STATIC_ATTN_MAX_RECORDS = 16384
 
 
 class Config(C.Structure):
@@ -107,6 +109,7 @@ def load() -> C.CDLL:
     lib.arcb_attn_scratch_bytes.restype = i64
     lib.arcb_attn_scratch_bytes.argtypes = [i32, i32, i32]
     lib.arcb_op_decode_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]
+    lib.arcb_op_decode_attention_static.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.arcb_op_head.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, f32, vp]
     _lib = lib
     return lib

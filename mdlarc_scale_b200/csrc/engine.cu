@@ -20,6 +20,8 @@ static std::atomic<long long> g_launches{0};
 
 void arcb_count_launch(long long n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
+void arcb_set_last_error(const char* msg) { g_last_error = msg ? msg : ""; }
+
 static int fail(int code, const char* msg) {
   g_last_error = msg;
   return code;
