@@ -33,6 +33,11 @@ sys.path.insert(0, str(ROOT))
 MAX_NEW = 931
 KV_POSITIONS = 1536
 MODEL_SIZE = "large"
+# DRAM traffic of the decode-attention kernel relative to its algorithmic bytes, from the ncu
+# capture summarised in profiles/attn_stream_kernel_ncu_full.md (256 sequences x 1000 cached
+# positions: 1311.40 MB read + 3.6 MB written per launch for 1310.72 MB algorithmic); traffic grows
+# in proportion to the cached positions, so a full-size launch is scaled by its algorithmic bytes.
+ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0033
 
 
 def measured_peaks():
@@ -98,17 +103,18 @@ def make_batch(seed: int, n: int):
 
 
 def model_state():
-    from oracle import arc_model as om  # weight initialiser only (seeded random-init, reference distributions)
-    cfg = om.make_config(MODEL_SIZE, max_seq_len=4096)
-    return cfg, om.round_bf16(om.init_state(cfg, seed=0))
+    """Seeded random-init weights of the large model (reference distributions), rounded to bf16."""
+    from mdlarc_scale_b200.synthetic import seeded_weights
+    return seeded_weights(MODEL_SIZE, seed=0)
 
 
 # ---------------------------------------------------------------------------
 # CPU baseline / reference arm: the oracle port of generate_output on the host cores
 # ---------------------------------------------------------------------------
 def cpu_generate_sample(n_seqs: int, n_steps: int, seed: int):
-    from oracle import arc_model as om
-    cfg, sd = model_state()
+    from oracle import arc_model as om  # the timed CPU baseline IS the oracle port
+    cfg_d, sd = model_state()
+    cfg = om.Config(**cfg_d)
     ids, pos, mask = make_batch(seed, n_seqs)
     t0 = time.perf_counter()
     r = om.generate(sd, cfg, torch.from_numpy(ids), torch.from_numpy(pos), None, torch.from_numpy(mask),
@@ -180,6 +186,33 @@ def attention_roofline(engine, session, lens0: np.ndarray, n_layers_sampled: int
             bytes_.append(algo)
     gbs = float(np.mean([b / t for b, t in zip(bytes_, times)]) / 1e9)
     return gbs, float(np.mean(times) * 1e3), float(np.mean(bytes_))
+
+
+def profile_attention(args):
+    """Standalone decode-attention launches of known size for an ncu capture: `--batch` sequences,
+    20 heads, every sequence `--profile-attn` cached positions; prints the algorithmic bytes."""
+    from mdlarc_scale_b200 import _lib
+    lib = _lib.load()
+    B, H, T = args.batch, 20, args.profile_attn
+    dev = torch.device("cuda", 0)
+    q = torch.randn(B, H, 64, device=dev).to(torch.float16)
+    kv = torch.randn(2, B, H, T, 64, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+    ms = []
+    for _ in range(4):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(lib.arcb_op_decode_attention(q.data_ptr(), kv[0].data_ptr(), kv[1].data_ptr(), out.data_ptr(), None,
+                                                lens.data_ptr(), None, B, H, T, 1, None, _lib.ACT_F16,
+                                                torch.cuda.current_stream(dev).cuda_stream))
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    algo = B * H * T * 64 * 2 * 2
+    print(json.dumps({"profile": "decode attention", "batch": B, "heads": H, "cached_positions": T,
+                      "algorithmic_bytes_per_launch": algo, "ms_per_launch": ms,
+                      "gbs_last": algo / ms[-1] / 1e6}))
 
 
 def run_ours(args, rank, world, local_rank):
@@ -311,7 +344,7 @@ def run_ours(args, rank, world, local_rank):
             "gpu_launches": launches,
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": attn_gbs, "peak": peak, "unit": "GB/s",
-                         "frac": attn_gbs / peak, "traffic": None, "peak_kind": peak_kind,
+                         "frac": attn_gbs / peak, "traffic": attn_bytes * ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE, "peak_kind": peak_kind,
                          "kernel": "attn_stream_kernel (decode attention)", "ms_per_launch": attn_ms,
                          "algorithmic_bytes_per_launch": attn_bytes},
             "prefill": {"tokens_per_s_per_gpu": prefill_tok_s, "tokens_per_step": prefill_tokens // args.steps},
@@ -341,6 +374,8 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=48)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--profile-attn", type=int, default=0, metavar="T",
+                    help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
     ap.add_argument("--max-new", type=int, default=MAX_NEW,
                     help="tokens generated per sequence (the workload uses 931; smaller only for profiling)")
     args = ap.parse_args()
@@ -353,6 +388,9 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a B200 GPU (the product path has no CPU fallback)")
+    if args.profile_attn > 0:
+        profile_attention(args)
+        return
     run_ours(args, rank, world, local_rank)
 
 

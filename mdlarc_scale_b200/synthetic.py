@@ -73,3 +73,38 @@ def config_prompts(cfg_idx: int, n_tasks: int | None = None, seed: int | None = 
     tasks = capped_tasks(cfg_idx if seed is None else seed, n_tasks or c["n_tasks"], c["k"][0], c["k"][1],
                          c["hw"][0], c["hw"][1], c["cap"])
     return tasks, prompts_for(tasks, c["dihedrals"])
+
+
+def seeded_weights(size: str, seed: int = 0, embed_gain: float = 1.0):
+    """Seeded random-init weights with the reference's distributions (src/transformer.py:547-560),
+    rounded to bf16; ``embed_gain`` > 1 makes generations varied enough to reach END."""
+    import math
+
+    import torch
+    dims = {"tiny": (256, 4, 4, 704), "small": (768, 12, 4, 2048), "medium": (1024, 16, 8, 2752),
+            "large": (1280, 20, 12, 3392)}[size]
+    d, h, L, dff = dims
+    g = torch.Generator().manual_seed(seed)
+
+    def xavier(o, i):
+        return (torch.rand(o, i, generator=g) * 2 - 1) * math.sqrt(6.0 / (i + o))
+
+    sd = {"token_embed.weight": torch.randn(14, d, generator=g) * 0.02 * embed_gain,
+          "example_embed.weight": torch.randn(1280, d, generator=g) * 0.02}
+    for l in range(L):
+        p = f"blocks.{l}."
+        sd[p + "ln1.weight"] = torch.ones(d)
+        sd[p + "attn.qkv_proj.weight"] = xavier(3 * d, d)
+        sd[p + "attn.out_proj.weight"] = xavier(d, d)
+        sd[p + "ln2.weight"] = torch.ones(d)
+        sd[p + "ffn.fc_gate.weight"] = xavier(dff, d)
+        sd[p + "ffn.fc_gate.bias"] = torch.zeros(dff)
+        sd[p + "ffn.fc_up.weight"] = xavier(dff, d)
+        sd[p + "ffn.fc_up.bias"] = torch.zeros(dff)
+        sd[p + "ffn.fc_down.weight"] = xavier(d, dff)
+        sd[p + "ffn.fc_down.bias"] = torch.zeros(d)
+    sd["ln_f.weight"] = torch.ones(d)
+    sd["lm_head.weight"] = xavier(14, d)
+    cfg = dict(d_model=d, n_heads=h, n_layers=L, d_ff=dff, vocab_size=14, max_seq_len=4096, num_examples=1280,
+               max_x=32, max_y=32, max_z=8, rope_base=10000.0, norm_eps=1e-5, use_example_embedding=True)
+    return cfg, {k: v.to(torch.bfloat16).float() for k, v in sd.items()}
