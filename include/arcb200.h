@@ -154,11 +154,11 @@ typedef struct arcb_prefill_args {
   const int32_t* d_kv_count;   /* [n_tokens]                                   */
   const int32_t* d_example_ids; /* [B] indexed by cache row (NULL = no example embedding) */
   /* tensor-core prefill attention work list (optional; without it the streaming kernel runs):
-   * query blocks of <= 128 consecutive rows of one sequence, and where each row's K/V goes in
+   * query blocks of <= 256 consecutive rows of one sequence, and where each row's K/V goes in
    * the call's contiguous 16-bit K/V scratch (a sequence's keys are consecutive rows in slot order) */
   int32_t n_qblocks;
   const int32_t* d_qblock_row0; /* [n_qblocks] first packed row                */
-  const int32_t* d_qblock_rows; /* [n_qblocks] rows in block (1..128)          */
+  const int32_t* d_qblock_rows; /* [n_qblocks] rows in block (1..256)          */
   const int32_t* d_qblock_kv0;  /* [n_qblocks] first scratch row of the block's sequence */
   const int32_t* d_kv_row;      /* [n_tokens] scratch row of the token's K/V, < 0: none  */
   int32_t n_kv_rows;            /* scratch rows written by this call (all in [0, n_kv_rows)) */

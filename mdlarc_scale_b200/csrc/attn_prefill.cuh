@@ -10,7 +10,7 @@ struct AttnPrefillArgs {
   const int* seq;           // [n_rows] cache row of each packed row
   const int* kv_count;      // [n_rows] attended prefix length
   const int* qblock_row0;   // [n_qblocks] first packed row of the block
-  const int* qblock_rows;   // [n_qblocks] rows in the block (1..128), all of one sequence
+  const int* qblock_rows;   // [n_qblocks] rows in the block (1..256), all of one sequence
   const int* qblock_kv0;    // [n_qblocks] first K/V scratch row of the block's sequence
   int n_qblocks, n_rows, n_kv_rows, n_heads;
   int act_f16;

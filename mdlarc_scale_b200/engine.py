@@ -320,7 +320,7 @@ def initial_grid_state(last_tok: np.ndarray, last_pos: np.ndarray, has_tokens: n
     return x.astype(np.int32), y.astype(np.int32), in_out.astype(np.int32)
 
 
-def _qblocks(seq_of_row: np.ndarray, block: int = 128):
+def _qblocks(seq_of_row: np.ndarray, block: int = 256):
     """Split consecutive rows of the same sequence into blocks of at most ``block`` rows."""
     n = len(seq_of_row)
     if n == 0:

@@ -184,3 +184,27 @@ def test_large_model_logits_within_tolerance():
         worst = max(worst, (tr.step_logits[b].cpu() - ref[len(p) - 1: len(p) - 1 + n_new]).abs().max().item())
     assert worst < TOL, f"large model: max abs decode-step logit error {worst}"
     eng.close()
+
+
+def test_flash_prefill_long_prompts(engines):
+    """Prompts of 700-1900 tokens (several 128-key tiles, both Q tiles of a 256-row block, ragged
+    tails): tensor-core flash prefill vs the streaming kernel and vs the fp32 oracle."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import pad_prompts
+    from mdlarc_scale_b200.transformer import forward_logits
+    flash, cfg, sd = engines["varied", "tc-flash"]
+    stream_eng = engines["varied", "tc-stream"][0]
+    tasks = synthetic.capped_tasks(61, 3, 2, 4, 8, 16, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    assert max(len(p) for p in prompts) > 600
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
+    ex = torch.tensor([1, 2, 3])
+    a = forward_logits(flash, ids_t, pos_t, ex, mask_t).cpu()
+    b = forward_logits(stream_eng, ids_t, pos_t, ex, mask_t).cpu()
+    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
+    e_flash = (a[mask_t] - want[mask_t]).abs().max().item()
+    e_stream = (b[mask_t] - want[mask_t]).abs().max().item()
+    e_ab = (a[mask_t] - b[mask_t]).abs().max().item()
+    print(f"long prompts: flash-oracle {e_flash:.4f} stream-oracle {e_stream:.4f} flash-stream {e_ab:.4f}")
+    assert e_flash < TOL and e_stream < TOL and e_ab < TOL, (e_flash, e_stream, e_ab)
