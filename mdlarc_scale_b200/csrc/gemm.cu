@@ -1,8 +1,9 @@
 // y = A[M,K] * W[N,K]^T, both operands in the same 16-bit format (half or bfloat16: tcgen05
 // kind::f16 rejects mixed A/B formats with an illegal-instruction fault), fp32 accumulate, with the
 // fused epilogues of epilogue.cuh.  Two kernels:
-//   gemm_tc_kernel   : tcgen05.mma (UMMA 128xBNx16, accumulator in TMEM), operands
-//                      staged by TMA (128-byte swizzle) through an mbarrier ring;
+//   gemm_tc_kernel   : persistent; tcgen05.mma (UMMA 128x256x16 or 128x128x16), two fp32
+//                      accumulators in TMEM (the epilogue drains one while the next tile fills the
+//                      other), operands staged by TMA (128-byte swizzle) through an mbarrier ring;
 //                      warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.
 //   gemm_simt_kernel : CUDA-core tile kernel for skinny M (weight streaming) and as
 //                      the cross-check of the tensor-core path.
@@ -21,32 +22,36 @@ constexpr int TC_BK = 64;  // 64 x 2 B = one 128-byte swizzle row
 
 template <int BN>
 struct TcCfg {
-  static constexpr int STAGES = (BN == 128) ? 3 : 4;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;
   static constexpr int B_BYTES = BN * TC_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  // stages + barriers (full, empty per stage, acc) + tmem slot, + 1024 alignment slack
+  static constexpr int TMEM_COLS = 2 * BN;  // two accumulators: the epilogue drains one while the MMA fills the other
+  // stages + barriers (full, empty per stage; acc_full, acc_empty x2) + tmem slot, + 1024 alignment slack
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+// Persistent kernel: CTA c processes output tiles c, c + gridDim.x, ... (n fastest, so the CTAs
+// running at the same time share A rows through L2).  The TMA->MMA shared-memory ring runs
+// continuously across tiles; accumulators alternate between two TMEM buffers.
 template <int BN, int MODE>
 __global__ void __launch_bounds__(192, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               GemmEpilogue ep, int K, uint32_t idesc) {
+               GemmEpilogue ep, int K, uint32_t idesc, int tiles_n, int tiles_total) {
   using Cfg = TcCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t bar_base = base + Cfg::STAGES * Cfg::STAGE_BYTES;
-  // full[s] at bar_base + 8*s, empty[s] at bar_base + 8*(STAGES+s), acc at + 16*STAGES
-  const uint32_t bar_acc = bar_base + 16 * Cfg::STAGES;
+  // full[s] at +8s, empty[s] at +8(STAGES+s), acc_full[2], acc_empty[2] after them
+  const uint32_t bar_acc_full = bar_base + 16 * Cfg::STAGES;
+  const uint32_t bar_acc_empty = bar_acc_full + 16;
   volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 16 * Cfg::STAGES + 8);
+      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 16 * Cfg::STAGES + 32);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_blk = blockIdx.x, m_blk = blockIdx.y;
   const int num_k = K / TC_BK;
 
   if (threadIdx.x == 0) {
@@ -54,14 +59,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(bar_base + 8 * s, 1);
       mbar_init(bar_base + 8 * (Cfg::STAGES + s), 1);
     }
-    mbar_init(bar_acc, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 128);
+    }
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), BN);
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -72,63 +80,82 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 0) {
     // ---- TMA producer ----
     if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % Cfg::STAGES;
-        const uint32_t ph = (kb / Cfg::STAGES) & 1;
-        if (!mbar_wait_bounded(bar_base + 8 * (Cfg::STAGES + s), ph ^ 1)) {
-          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_MMA);
-          *abort_flag = 1;
-          break;
+      uint32_t kbt = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x) {
+        const int m_blk = tile / tiles_n, n_blk = tile - m_blk * tiles_n;
+        for (int kb = 0; kb < num_k; ++kb, ++kbt) {
+          const int s = kbt % Cfg::STAGES;
+          const uint32_t ph = (kbt / Cfg::STAGES) & 1;
+          if (!mbar_wait_bounded(bar_base + 8 * (Cfg::STAGES + s), ph ^ 1)) {
+            arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_MMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          if (*abort_flag) { ok = false; break; }
+          const uint32_t full = bar_base + 8 * s;
+          const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(full, Cfg::STAGE_BYTES);
+          tma_load_2d(a_dst, &tmap_a, kb * TC_BK, m_blk * TC_BM, full);
+          tma_load_2d(a_dst + Cfg::A_BYTES, &tmap_b, kb * TC_BK, n_blk * BN, full);
         }
-        if (*abort_flag) break;
-        const uint32_t full = bar_base + 8 * s;
-        const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
-        mbar_expect_tx(full, Cfg::STAGE_BYTES);
-        tma_load_2d(a_dst, &tmap_a, kb * TC_BK, m_blk * TC_BM, full);
-        tma_load_2d(a_dst + Cfg::A_BYTES, &tmap_b, kb * TC_BK, n_blk * BN, full);
-        ++issued;
       }
-      (void)issued;
     }
   } else if (warp == 1) {
     // ---- MMA issuer ----
     if (lane == 0) {
+      uint32_t kbt = 0, it = 0;
       bool ok = true;
-      for (int kb = 0; kb < num_k; ++kb) {
-        const int s = kb % Cfg::STAGES;
-        const uint32_t ph = (kb / Cfg::STAGES) & 1;
-        if (!mbar_wait_bounded(bar_base + 8 * s, ph)) {
-          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
+      for (int tile = blockIdx.x; ok && tile < tiles_total; tile += gridDim.x, ++it) {
+        const uint32_t acc = it & 1;
+        // wait until the epilogue has drained this accumulator (two tiles ago)
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * acc, ((it >> 1) & 1) ^ 1)) {
+          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
           *abort_flag = 1;
-          ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t a_addr = base + s * Cfg::STAGE_BYTES;
-        const uint64_t da = umma_desc_k_sw128(a_addr);
-        const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++kbt) {
+          const int s = kbt % Cfg::STAGES;
+          const uint32_t ph = (kbt / Cfg::STAGES) & 1;
+          if (!mbar_wait_bounded(bar_base + 8 * s, ph)) {
+            arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = base + s * Cfg::STAGE_BYTES;
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
 #pragma unroll
-        for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
-          // +32 bytes per K step of 16 elements -> +2 in the (addr >> 4) field
-          umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) ? 1u : 0u);
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4) {
+            // +32 bytes per K step of 16 elements -> +2 in the (addr >> 4) field
+            umma_f16(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) ? 1u : 0u);
+          }
+          umma_commit(bar_base + 8 * (Cfg::STAGES + s));  // frees the stage when the MMAs retire
         }
-        umma_commit(bar_base + 8 * (Cfg::STAGES + s));  // frees the stage when the MMAs retire
+        if (ok) umma_commit(bar_acc_full + 8 * acc);
       }
-      if (ok) umma_commit(bar_acc);
     }
   } else {
     // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
-    const int m = m_blk * TC_BM + row_in_tile;
-    const bool row_ok = m < ep.M;
-    bool ok = mbar_wait_bounded(bar_acc, 0);
-    if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    uint32_t it = 0;
+    for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++it) {
+      const int m_blk = tile / tiles_n, n_blk = tile - m_blk * tiles_n;
+      const uint32_t acc = it & 1;
+      const int m = m_blk * TC_BM + row_in_tile;
+      const bool row_ok = m < ep.M;
+      bool ok = mbar_wait_bounded(bar_acc_full + 8 * acc, (it >> 1) & 1);
+      if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
       RopeRow rr;
       rr.x = rr.y = rr.z = 0;
       rr.kv_row = -1;
@@ -138,6 +165,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         // gate columns [0,64) and up columns [64,128) of every 128-column group
 #pragma unroll 1
         for (int g0 = 0; g0 < BN; g0 += 128) {
+          if (n_blk * BN + g0 >= ep.N) break;  // warp-uniform: tile tail beyond N
 #pragma unroll 1
           for (int c = 0; c < 2; ++c) {
             uint32_t rg[32], ru[32];
@@ -160,11 +188,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
+          const int n0 = n_blk * BN + c * 32;
+          if (n0 >= ep.N) break;  // warp-uniform
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_wait_ld();
           if (row_ok) {
-            const int n0 = n_blk * BN + c * 32;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
               const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
@@ -177,13 +206,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
       }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      mbar_arrive(bar_acc_empty + 8 * acc);
     }
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, BN);
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -312,9 +344,14 @@ bool arcb_gemm_tc_supported(int M, int N, int K) {
 
 template <int MODE>
 static cudaError_t set_tc_smem_attr() {
-  return cudaFuncSetAttribute(gemm_tc_kernel<128, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              TcCfg<128>::SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<128, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       TcCfg<128>::SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gemm_tc_kernel<256, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              TcCfg<256>::SMEM_BYTES);
 }
+
+static int g_num_sms = 0;
 
 // Opt in to the large dynamic shared memory of every tcgen05 instantiation (call once, outside
 // any stream capture).
@@ -324,7 +361,21 @@ int arcb_gemm_init() {
   if ((e = set_tc_smem_attr<EPI_QKV_ROPE>()) != cudaSuccess) return (int)e;
   if ((e = set_tc_smem_attr<EPI_RESID>()) != cudaSuccess) return (int)e;
   if ((e = set_tc_smem_attr<EPI_SWIGLU>()) != cudaSuccess) return (int)e;
+  int dev = 0;
+  if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+  if ((e = cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
   return get_encode_fn() ? 0 : -100;
+}
+
+template <int BN, int MODE>
+static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue& ep, int K, int act_f16,
+                      cudaStream_t stream) {
+  const int tiles_n = (ep.N + BN - 1) / BN, tiles_m = (ep.M + TC_BM - 1) / TC_BM;
+  const int tiles = tiles_n * tiles_m;
+  const int sms = g_num_sms > 0 ? g_num_sms : 148;
+  const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
+  gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, 192, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc,
+                                                                                            tiles_n, tiles);
 }
 
 template <int MODE>
@@ -332,15 +383,17 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
                             int act_f16, bool use_tc, cudaStream_t stream) {
   const int M = ep.M, N = ep.N;
   if (use_tc) {
-    constexpr int BN = 128;
+    // 128 x 256 tiles (one CTA per SM, persistent) unless that leaves most SMs without a tile
+    const int sms = g_num_sms > 0 ? g_num_sms : 148;
+    const int tiles256 = ((N + 255) / 256) * ((M + TC_BM - 1) / TC_BM);
+    const bool wide = tiles256 * 10 >= sms * 7;
     CUtensorMap ta, tb;
     int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
     if (r) return 1000 + r;
-    r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, BN, TC_BK, act_f16);
+    r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, wide ? 256 : 128, TC_BK, act_f16);
     if (r) return 1000 + r;
-    const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
-    dim3 grid(N / BN, (M + TC_BM - 1) / TC_BM);
-    gemm_tc_kernel<BN, MODE><<<grid, 192, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc);
+    if (wide) launch_tc<256, MODE>(ta, tb, ep, K, act_f16, stream);
+    else launch_tc<128, MODE>(ta, tb, ep, K, act_f16, stream);
   } else {
     dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
     gemm_simt_kernel<MODE><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a16),

@@ -33,7 +33,8 @@ def test_rmsnorm(lib, fmt, rows, d):
 @pytest.mark.parametrize("path", [_lib.GEMM_SIMT, _lib.GEMM_TC], ids=["simt", "tc"])
 @pytest.mark.parametrize("fmt", [_lib.ACT_BF16, _lib.ACT_F16], ids=["bf16", "f16"])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 768, 256), (33, 256, 704), (128, 384, 128),
-                                   (300, 1408, 256), (1000, 1280, 3392)])
+                                   (300, 1408, 256), (1000, 1280, 3392),
+                                   (2048, 3840, 256), (4000, 6784, 128), (20000, 1280, 192)])
 def test_gemm(lib, path, fmt, M, N, K):
     g = torch.Generator(device="cuda").manual_seed(M + N + K)
     a = to_act(torch.randn(M, K, device="cuda", generator=g), fmt)

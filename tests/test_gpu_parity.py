@@ -208,3 +208,30 @@ def test_flash_prefill_long_prompts(engines):
     e_ab = (a[mask_t] - b[mask_t]).abs().max().item()
     print(f"long prompts: flash-oracle {e_flash:.4f} stream-oracle {e_stream:.4f} flash-stream {e_ab:.4f}")
     assert e_flash < TOL and e_stream < TOL and e_ab < TOL, (e_flash, e_stream, e_ab)
+
+
+def test_small_model_many_tokens_wide_gemm_tiles():
+    """Small model (d 768, 12 heads, 4 layers, d_ff 2048) on ~6000 packed prompt tokens: every
+    linear runs on the 128x256 tensor-core tiles (QKV/RoPE, residual and SwiGLU epilogues, and a
+    ragged last tile), checked against the fp32 oracle on all positions."""
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import pad_prompts
+    from mdlarc_scale_b200.transformer import forward_logits
+    cfg = om.make_config("small", max_seq_len=4096)
+    sd = om.round_bf16(om.perturb_state(om.init_state(cfg, seed=3), seed=4))
+    eng = Engine(sd, cfg, "cuda:0")
+    tasks = synthetic.capped_tasks(71, 6, 2, 3, 10, 15, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    assert sum(len(p) for p in prompts) > 4600
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
+    ex = torch.arange(len(prompts))
+    got = forward_logits(eng, ids_t, pos_t, ex, mask_t).cpu()
+    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
+    err = (got[mask_t] - want[mask_t]).abs().max().item()
+    print(f"small model, {int(mask.sum())} tokens: max abs logit error {err:.4f}")
+    assert err < TOL
+    eng.close()
