@@ -215,6 +215,46 @@ def profile_attention(args):
                       "gbs_last": algo / ms[-1] / 1e6}))
 
 
+def profile_prefill(args):
+    """Prefill-only pass of the prefill-heavy large configuration: prompts of `--profile-prefill`
+    train pairs of 30x30 grids plus a 30x30 test input (5 pairs = 10 247 tokens), about 64k packed
+    tokens per call; prints prompt tokens/s and the algorithmic TFLOP/s (linear 469.9 MFLOP per
+    token + causal attention 2*d*L*len^2 per sequence)."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine, chunk_rows, plan_prefill
+    from mdlarc_scale_b200.inference import pad_prompts
+    dev = torch.device("cuda", 0)
+    cfg, sd = model_state()
+    cfg["max_seq_len"] = 16384
+    engine = Engine(sd, cfg, dev)
+    k = args.profile_prefill
+    n = max(1, 64000 // (1863 * k + 932))
+    tasks = synthetic.capped_tasks(3, n, k, k, 30, 30, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    lens = mask.sum(axis=1)
+    cap = 65536
+    sess = engine.new_session(n, int(lens.max()) + 8, 8, cap, stop_on_end=False)
+    plans = [plan_prefill(ids, pos, mask, r).to(dev) for r in chunk_rows(lens, cap)]
+    ms = []
+    for _ in range(args.warmup + args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for p in plans:
+            sess.prefill(p, None)
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+    sess.poll()
+    t = float(np.mean(ms[args.warmup:])) / 1e3
+    ntok = int(lens.sum())
+    lin = ntok * 469.9e6
+    att = float((2.0 * 1280 * 12 * lens.astype(np.float64) ** 2).sum())
+    print(json.dumps({"profile": "prefill", "pairs": k, "sequences": n, "tokens": ntok, "max_len": int(lens.max()),
+                      "ms": t * 1e3, "tokens_per_s": ntok / t, "linear_tflop": lin / 1e12, "attention_tflop": att / 1e12,
+                      "tflops": (lin + att) / t / 1e12, "frac_of_bf16_burst_peak": (lin + att) / t / 1e12 / 1672.1}))
+
+
 def run_ours(args, rank, world, local_rank):
     from mdlarc_scale_b200 import _lib
     from mdlarc_scale_b200.engine import Engine, chunk_rows, plan_prefill
@@ -376,6 +416,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--profile-attn", type=int, default=0, metavar="T",
                     help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
+    ap.add_argument("--profile-prefill", type=int, default=0, metavar="PAIRS",
+                    help="only time the prefill of ~64k tokens of prompts with PAIRS 30x30 train pairs")
     ap.add_argument("--max-new", type=int, default=MAX_NEW,
                     help="tokens generated per sequence (the workload uses 931; smaller only for profiling)")
     args = ap.parse_args()
@@ -390,6 +432,9 @@ def main():
         raise SystemExit("bench.py needs a B200 GPU (the product path has no CPU fallback)")
     if args.profile_attn > 0:
         profile_attention(args)
+        return
+    if args.profile_prefill > 0:
+        profile_prefill(args)
         return
     run_ours(args, rank, world, local_rank)
 

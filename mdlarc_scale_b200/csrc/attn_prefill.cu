@@ -53,6 +53,14 @@ __device__ __forceinline__ uint32_t pack2_prob(float a, float b, int f16) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// 2^x on the special-function unit, one instruction (flushes denormals; inputs here are <= 0 or
+// masked afterwards)
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 struct Bars {
   uint32_t q, kv_full, kv_empty, s[2], p[2], o[2];
 };
@@ -249,22 +257,35 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_fence_after();
       const int n_valid = min(max(my_cnt - j * BKV, 0), BKV);   // visible keys of this row in the tile
       const bool full = __all_sync(0xffffffffu, n_valid == BKV);
+      // Both passes keep the tcgen05.ld of the next 32-column chunk in flight while the current
+      // chunk is processed (two register buffers).
+      uint32_t sbuf[2][32];
       // pass 1: row maximum of the visible raw scores
-      float mx = -INFINITY;
-#pragma unroll 1
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      tmem_ld_32x32(t_s, sbuf[0]);
+      tmem_wait_ld_dep(sbuf[0]);
+#pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t sreg[32];
-        tmem_ld_32x32(t_s + c * 32, sreg);
-        tmem_wait_ld();
+        uint32_t (&cur)[32] = sbuf[c & 1];
+        // chunk c+1 of this pass, or chunk 0 of pass 2 (the scores are read twice)
+        tmem_ld_32x32(t_s + ((c + 1) & 3) * 32, sbuf[(c + 1) & 1]);
+        // four independent running maxima keep the dependency chains short
         if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+          for (int i = 0; i < 32; i += 4) {
+            mx4[0] = fmaxf(mx4[0], __uint_as_float(cur[i]));
+            mx4[1] = fmaxf(mx4[1], __uint_as_float(cur[i + 1]));
+            mx4[2] = fmaxf(mx4[2], __uint_as_float(cur[i + 2]));
+            mx4[3] = fmaxf(mx4[3], __uint_as_float(cur[i + 3]));
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < n_valid) mx = fmaxf(mx, __uint_as_float(sreg[i]));
+            if (c * 32 + i < n_valid) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(cur[i]));
         }
+        tmem_wait_ld_dep(sbuf[(c + 1) & 1]);
       }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m, mx * sc);
       const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
       if (j > 0) {
@@ -272,30 +293,31 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         if (!ok) break;
       }
       const float alpha = exp2f(m - m_safe);
-      float lsum = 0.f;
-      // pass 2: probabilities -> shared memory (swizzled K-major, 16-bit)
-#pragma unroll 1
+      float ls0 = 0.f, ls1 = 0.f;
+      // pass 2: probabilities -> shared memory (swizzled K-major, 16-bit); sbuf[0] holds chunk 0
+#pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t sreg[32];
-        tmem_ld_32x32(t_s + c * 32, sreg);
-        tmem_wait_ld();
+        uint32_t (&cur)[32] = sbuf[c & 1];
+        if (c + 1 < BKV / 32) tmem_ld_32x32(t_s + (c + 1) * 32, sbuf[(c + 1) & 1]);
         uint32_t pk[16];
         if (full) {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(sreg[i]), sc, -m_safe));
-            const float p1 = exp2f(fmaf(__uint_as_float(sreg[i + 1]), sc, -m_safe));
-            lsum += p0 + p1;
+            const float p0 = ex2_fast(fmaf(__uint_as_float(cur[i]), sc, -m_safe));
+            const float p1 = ex2_fast(fmaf(__uint_as_float(cur[i + 1]), sc, -m_safe));
+            ls0 += p0;
+            ls1 += p1;
             pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float p0 = exp2f(fmaf(__uint_as_float(sreg[i]), sc, -m_safe));
-            float p1 = exp2f(fmaf(__uint_as_float(sreg[i + 1]), sc, -m_safe));
+            float p0 = ex2_fast(fmaf(__uint_as_float(cur[i]), sc, -m_safe));
+            float p1 = ex2_fast(fmaf(__uint_as_float(cur[i + 1]), sc, -m_safe));
             if (c * 32 + i >= n_valid) p0 = 0.f;
             if (c * 32 + i + 1 >= n_valid) p1 = 0.f;
-            lsum += p0 + p1;
+            ls0 += p0;
+            ls1 += p1;
             pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
           }
         }
@@ -308,8 +330,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           *reinterpret_cast<uint4*>(tile + ch * 16) =
               make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
         }
+        if (c + 1 < BKV / 32) tmem_wait_ld_dep(sbuf[(c + 1) & 1]);
       }
-      l = l * alpha + lsum;
+      l = l * alpha + (ls0 + ls1);
       m = m_new;
       alpha_pending = alpha;
       // make the generic-proxy writes of P visible to the tensor-core (async) proxy
