@@ -2,14 +2,18 @@
 //
 // One CTA = up to 256 consecutive query rows of one sequence (two 128-row Q tiles, A and B) x one
 // head.  Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax
-// group of tile A, warps 6-9 softmax group of tile B.  Per 128-key tile j:
+// group of tile A, warps 6-9 softmax group of tile B (one thread per query row).  Per 128-key tile j:
 //   TMA        K and V tiles [128 keys][64 dims], 128-byte swizzle, 3-stage ring shared by A and B
 //   MMA        S_x = Q_x K^T   (UMMA 128x128x16 x4, fp32 in TMEM)            x in {A, B}
-//   softmax_x  one thread per query row: row max (tcgen05.ld), then p = exp2(s*c - m) written
-//              16-bit into shared memory in the swizzled K-major layout the MMA reads
-//   MMA        Otile_x = P_x V (UMMA 128x64x16 x8, V is the MN-major B operand), into one of two
-//              TMEM buffers, so the softmax thread folds Otile(j-1) into its register-resident
-//              output row while the tensor core is already busy with tile j
+//   softmax_x  the row's 128 scores are read once from TMEM into registers; row max;
+//              p = exp2(s*c - m_ref) written 16-bit into shared memory in the swizzled K-major
+//              layout the MMA reads
+//   MMA        O_x += P_x V    (UMMA 128x64x16 x8, V is the MN-major B operand), accumulated in
+//              TMEM across all tiles
+// The reference maximum m_ref of a row is only raised when the true maximum exceeds it by more
+// than 8 (in log2 units), so p <= 256 stays well inside the 16-bit range and the accumulated O
+// rarely needs rescaling; when it does, the row's thread rescales O in TMEM before releasing P.
+// The final 1/l normalisation makes the result independent of m_ref.
 // The two groups run out of phase: the tensor core works on one Q tile while the other group's
 // threads do exponentials.  Rows carry their own visible-key count (causal AND key padding as a
 // prefix length), so no mask tensor exists.  Q, K, V and P share one 16-bit format (kind::f16
@@ -28,9 +32,10 @@ constexpr int KV_TILE_BYTES = BKV * HD * 2;   // 16 KB each for K and V
 constexpr int P_BYTES = BQ * BKV * 2;         // 32 KB per Q tile: two [128][64] swizzled K-major tiles
 constexpr int KV_STAGES = 3;
 constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 2 * P_BYTES + 1024 + 256;
-constexpr int TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A0 [256,320) O_A1 [320,384) O_B0 [384,448) O_B1 [448,512)
+constexpr int TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int N_THREADS = 320;
+constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 // MN-major operand tile [K rows of 128 bytes][64 elements], 128-byte swizzle: 8-row groups are
 // 1024 bytes apart along K (stride byte offset); a single 64-element group along MN.
@@ -62,7 +67,7 @@ __device__ __forceinline__ float ex2_fast(float x) {
 }
 
 struct Bars {
-  uint32_t q, kv_full, kv_empty, s[2], p[2], o[2];
+  uint32_t q, kv_full, kv_empty, s[2], p[2], o[2], sfree[2];
 };
 
 __global__ void __launch_bounds__(N_THREADS, 1)
@@ -89,6 +94,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   B.p[1] = B.s[0] + 24;
   B.o[0] = B.s[0] + 32;
   B.o[1] = B.s[0] + 40;
+  B.sfree[0] = B.s[0] + 48;
+  B.sfree[1] = B.s[0] + 56;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(p_ptr + 2 * P_BYTES + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,6 +126,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(B.s[x], 1);
       mbar_init(B.p[x], 128);
       mbar_init(B.o[x], 1);
+      mbar_init(B.sfree[x], 128);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmap_q);
@@ -164,11 +172,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (!ok) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
       const uint64_t dq[2] = {umma_desc_k_sw128(q_smem), umma_desc_k_sw128(q_smem + Q_BYTES)};
       const int n_x[2] = {n_a, n_b};
-      auto wait_kv = [&](int j) -> bool {
-        if (mbar_wait_bounded(B.kv_full + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1)) return true;
-        arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
-        return false;
-      };
       auto mma_s = [&](int x, int j) {  // S_x = Q_x K(j)^T
         const uint64_t dk = umma_desc_k_sw128(kv_smem + (j % KV_STAGES) * 2 * KV_TILE_BYTES);
 #pragma unroll
@@ -176,43 +179,50 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           umma_f16(tmem_base + x * 128, dq[x] + 2 * ks, dk + 2 * ks, idesc_qk, ks ? 1u : 0u);
         umma_commit(B.s[x]);
       };
-      auto mma_o = [&](int x, int j) -> bool {  // Otile_x[j & 1] = P_x V(j)
-        if (!mbar_wait_bounded(B.p[x], j & 1)) {
-          arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-          return false;
-        }
-        tc_fence_after();
+      auto mma_o = [&](int x, int j) {  // O_x (+)= P_x V(j)
         const uint64_t dv = umma_desc_mn_sw128(kv_smem + (j % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES);
-        const uint32_t d_o = tmem_base + 256 + x * 128 + (j & 1) * 64;
+        const uint32_t d_o = tmem_base + 256 + x * 64;
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks) {
           const uint64_t dp = umma_desc_k_sw128(p_smem + x * P_BYTES + (ks >> 2) * (BQ * 128)) + 2 * (ks & 3);
           // 16 keys = 16 rows of 128 bytes = 2048 bytes further into the V tile
-          umma_f16(d_o, dp, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, ks ? 1u : 0u);
+          umma_f16(d_o, dp, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (j | ks) ? 1u : 0u);
         }
         umma_commit(B.o[x]);
-        return true;
       };
-      if (ok) ok = wait_kv(0);
-      if (ok) {
-        tc_fence_after();
-        if (n_x[0] > 0) mma_s(0, 0);
-      }
-      for (int j = 0; ok && j < n_tiles; ++j) {
-        if (j < n_x[1]) mma_s(1, j);
-        if (j < n_x[0]) ok = mma_o(0, j);
-        if (ok && j + 1 < n_x[0]) {
-          ok = wait_kv(j + 1);
-          if (ok) {
+      // Event-driven issue: S_x(j+1) as soon as the softmax threads have copied S_x(j) out of TMEM
+      // (sfree) and K(j+1) has landed; O_x += P_x V(j) as soon as P_x(j) is published.  A K/V stage
+      // is released once both Q tiles have issued their PV product on it.
+      int next_s[2] = {0, 0}, next_o[2] = {0, 0}, released = 0;
+      const long long t0 = clock64();
+      while (ok && (next_o[0] < n_x[0] || next_o[1] < n_x[1])) {
+        bool progress = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int js = next_s[x];
+          if (js < n_x[x] && mbar_try_wait(B.kv_full + 8 * (js % KV_STAGES), (js / KV_STAGES) & 1) &&
+              (js == 0 || mbar_try_wait(B.sfree[x], (js - 1) & 1))) {
             tc_fence_after();
-            mma_s(0, j + 1);
+            mma_s(x, js);
+            next_s[x] = js + 1;
+            progress = true;
+          }
+          const int jo = next_o[x];
+          if (jo < n_x[x] && jo < next_s[x] && mbar_try_wait(B.p[x], jo & 1)) {
+            tc_fence_after();
+            mma_o(x, jo);
+            next_o[x] = jo + 1;
+            progress = true;
           }
         }
-        if (ok && j < n_x[1]) ok = mma_o(1, j);
-        if (ok) umma_commit(B.kv_empty + 8 * (j % KV_STAGES));
-        if (ok && j + 1 < n_tiles) {
-          ok = wait_kv(j + 1);
-          if (ok) tc_fence_after();
+        while (released < n_tiles && (released >= n_x[0] || next_o[0] > released) &&
+               (released >= n_x[1] || next_o[1] > released)) {
+          umma_commit(B.kv_empty + 8 * (released % KV_STAGES));
+          ++released;
+        }
+        if (!progress && clock64() - t0 > (1ll << 33)) {
+          arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+          ok = false;
         }
       }
     }
@@ -222,31 +232,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int n_mine = grp ? n_b : n_a;
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t t_s = t_lane + grp * 128;
-    const uint32_t t_o = t_lane + 256 + grp * 128;
+    const uint32_t t_o = t_lane + 256 + grp * 64;
     uint8_t* p_row = p_ptr + grp * P_BYTES + r * 128;
     const float sc = 0.125f * LOG2E;
-    float m = -INFINITY, l = 0.f, alpha_pending = 1.f;
-    float o[HD];
-#pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    // o = o * alpha + Otile(j): folded one tile late, so the PV MMA is off the critical path
-    auto fold = [&](int j) -> bool {
-      bool good = mbar_wait_bounded(B.o[grp], j & 1);
-      if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-      good = __all_sync(0xffffffffu, good);
-      if (!good) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
-        uint32_t oreg[32];
-        tmem_ld_32x32(t_o + (j & 1) * 64 + c * 32, oreg);
-        tmem_wait_ld();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c * 32 + i] = fmaf(o[c * 32 + i], alpha_pending, __uint_as_float(oreg[i]));
-      }
-      return true;
-    };
     for (int j = 0; j < n_mine; ++j) {
       if (ok && !mbar_wait_bounded(B.s[grp], j & 1)) {
         arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
@@ -257,69 +247,83 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_fence_after();
       const int n_valid = min(max(my_cnt - j * BKV, 0), BKV);   // visible keys of this row in the tile
       const bool full = __all_sync(0xffffffffu, n_valid == BKV);
-      // Both passes keep the tcgen05.ld of the next 32-column chunk in flight while the current
-      // chunk is processed (two register buffers).
-      uint32_t sbuf[2][32];
-      // pass 1: row maximum of the visible raw scores
+      // the row's 128 scores, read once
+      uint32_t sv[4][32];
+      tmem_ld_32x32(t_s, sv[0]);
+      tmem_ld_32x32(t_s + 32, sv[1]);
+      tmem_ld_32x32(t_s + 64, sv[2]);
+      tmem_ld_32x32(t_s + 96, sv[3]);
+      tmem_wait_ld_dep(sv[0]);
+      tmem_wait_ld_dep(sv[1]);
+      tmem_wait_ld_dep(sv[2]);
+      tmem_wait_ld_dep(sv[3]);
+      // S is in registers: the tensor core may overwrite it with the next tile's scores
+      tc_fence_before();
+      mbar_arrive(B.sfree[grp]);
+      // row maximum of the visible raw scores (four independent chains)
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-      tmem_ld_32x32(t_s, sbuf[0]);
-      tmem_wait_ld_dep(sbuf[0]);
 #pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t (&cur)[32] = sbuf[c & 1];
-        // chunk c+1 of this pass, or chunk 0 of pass 2 (the scores are read twice)
-        tmem_ld_32x32(t_s + ((c + 1) & 3) * 32, sbuf[(c + 1) & 1]);
-        // four independent running maxima keep the dependency chains short
+      for (int c = 0; c < 4; ++c) {
         if (full) {
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
-            mx4[0] = fmaxf(mx4[0], __uint_as_float(cur[i]));
-            mx4[1] = fmaxf(mx4[1], __uint_as_float(cur[i + 1]));
-            mx4[2] = fmaxf(mx4[2], __uint_as_float(cur[i + 2]));
-            mx4[3] = fmaxf(mx4[3], __uint_as_float(cur[i + 3]));
+            mx4[0] = fmaxf(mx4[0], __uint_as_float(sv[c][i]));
+            mx4[1] = fmaxf(mx4[1], __uint_as_float(sv[c][i + 1]));
+            mx4[2] = fmaxf(mx4[2], __uint_as_float(sv[c][i + 2]));
+            mx4[3] = fmaxf(mx4[3], __uint_as_float(sv[c][i + 3]));
           }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < n_valid) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(cur[i]));
+            if (c * 32 + i < n_valid) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
         }
-        tmem_wait_ld_dep(sbuf[(c + 1) & 1]);
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      const float m_new = fmaxf(m, mx * sc);
-      const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+      // raise the reference maximum only when it is far below the true one
+      float alpha = 1.f;
+      if (mx > m_ref + RESCALE_THRESHOLD) {  // also the first visible tile (m_ref = -inf)
+        alpha = (m_ref == -INFINITY) ? 0.f : ex2_fast(m_ref - mx);
+        m_ref = mx;
+      }
+      l *= alpha;
       if (j > 0) {
-        ok = fold(j - 1);  // also guarantees the PV MMA of tile j-1 no longer reads the P buffer
+        // PV(j-1) must have retired: it reads the P buffer written below and updates O
+        bool good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
+        if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+        ok = __all_sync(0xffffffffu, good);
         if (!ok) break;
+        tc_fence_after();
       }
-      const float alpha = exp2f(m - m_safe);
+      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+        // O of earlier tiles was accumulated against the old reference: rescale it in TMEM
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t oreg[32];
+          tmem_ld_32x32(t_o + c * 32, oreg);
+          tmem_wait_ld_dep(oreg);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+          tmem_st_32x32(t_o + c * 32, oreg);
+        }
+        tmem_wait_st();
+      }
+      const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
       float ls0 = 0.f, ls1 = 0.f;
-      // pass 2: probabilities -> shared memory (swizzled K-major, 16-bit); sbuf[0] holds chunk 0
+      // probabilities -> shared memory (swizzled K-major, 16-bit)
 #pragma unroll
       for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t (&cur)[32] = sbuf[c & 1];
-        if (c + 1 < BKV / 32) tmem_ld_32x32(t_s + (c + 1) * 32, sbuf[(c + 1) & 1]);
         uint32_t pk[16];
-        if (full) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float p0 = ex2_fast(fmaf(__uint_as_float(cur[i]), sc, -m_safe));
-            const float p1 = ex2_fast(fmaf(__uint_as_float(cur[i + 1]), sc, -m_safe));
-            ls0 += p0;
-            ls1 += p1;
-            pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2_fast(fmaf(__uint_as_float(cur[i]), sc, -m_safe));
-            float p1 = ex2_fast(fmaf(__uint_as_float(cur[i + 1]), sc, -m_safe));
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = ex2_fast(fmaf(__uint_as_float(sv[c][i]), sc, -m_safe));
+          float p1 = ex2_fast(fmaf(__uint_as_float(sv[c][i + 1]), sc, -m_safe));
+          if (!full) {
             if (c * 32 + i >= n_valid) p0 = 0.f;
             if (c * 32 + i + 1 >= n_valid) p1 = 0.f;
-            ls0 += p0;
-            ls1 += p1;
-            pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
           }
+          ls0 += p0;
+          ls1 += p1;
+          pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
         }
         // columns [c*32, c*32+32) of row r: tile = c / 2, 16-byte chunks ch0 .. ch0+3
         uint8_t* tile = p_row + (c >> 1) * (BQ * 128);
@@ -330,32 +334,42 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           *reinterpret_cast<uint4*>(tile + ch * 16) =
               make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
         }
-        if (c + 1 < BKV / 32) tmem_wait_ld_dep(sbuf[(c + 1) & 1]);
       }
-      l = l * alpha + (ls0 + ls1);
-      m = m_new;
-      alpha_pending = alpha;
+      l += ls0 + ls1;
       // make the generic-proxy writes of P visible to the tensor-core (async) proxy
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(B.p[grp]);
     }
+    // the accumulated output row
     if (ok && n_mine > 0) {
-      // the last tile's contribution: o = o * alpha_last + Otile(n-1)
-      ok = fold(n_mine - 1);
+      bool good = mbar_wait_bounded(B.o[grp], (n_mine - 1) & 1);
+      if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+      ok = __all_sync(0xffffffffu, good);
     }
     const int qr = grp * BQ + r;
-    if (qr < rows) {
-      const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
-      uint16_t* dst = reinterpret_cast<uint16_t*>(a.out16) + ((size_t)(row0 + qr) * a.n_heads + h) * HD;
+    const float inv = (ok && l > 0.f) ? 1.f / l : 0.f;
+    uint16_t* dst = reinterpret_cast<uint16_t*>(a.out16) + ((size_t)(row0 + qr) * a.n_heads + h) * HD;
 #pragma unroll
-      for (int i = 0; i < HD; i += 8) {
-        uint4 v;
-        v.x = pack2_act(o[i] * inv, o[i + 1] * inv, a.act_f16);
-        v.y = pack2_act(o[i + 2] * inv, o[i + 3] * inv, a.act_f16);
-        v.z = pack2_act(o[i + 4] * inv, o[i + 5] * inv, a.act_f16);
-        v.w = pack2_act(o[i + 6] * inv, o[i + 7] * inv, a.act_f16);
-        *reinterpret_cast<uint4*>(dst + i) = v;
+    for (int c = 0; c < HD / 32; ++c) {
+      uint32_t oreg[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) oreg[i] = 0u;
+      if (ok && n_mine > 0) {
+        tc_fence_after();
+        tmem_ld_32x32(t_o + c * 32, oreg);
+        tmem_wait_ld_dep(oreg);
+      }
+      if (qr < rows) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 v;
+          v.x = pack2_act(__uint_as_float(oreg[i]) * inv, __uint_as_float(oreg[i + 1]) * inv, a.act_f16);
+          v.y = pack2_act(__uint_as_float(oreg[i + 2]) * inv, __uint_as_float(oreg[i + 3]) * inv, a.act_f16);
+          v.z = pack2_act(__uint_as_float(oreg[i + 4]) * inv, __uint_as_float(oreg[i + 5]) * inv, a.act_f16);
+          v.w = pack2_act(__uint_as_float(oreg[i + 6]) * inv, __uint_as_float(oreg[i + 7]) * inv, a.act_f16);
+          *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+        }
       }
     }
   }
