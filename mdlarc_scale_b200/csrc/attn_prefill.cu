@@ -66,10 +66,19 @@ __device__ __forceinline__ float ex2_fast(float x) {
   return y;
 }
 
+// 2^x for two packed halves in one special-function instruction
+__device__ __forceinline__ __half2 ex2_half2(__half2 x) {
+  uint32_t xi = *reinterpret_cast<uint32_t*>(&x), yi;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(yi) : "r"(xi));
+  return *reinterpret_cast<__half2*>(&yi);
+}
+__device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+
 struct Bars {
   uint32_t q, kv_full, kv_empty, s[2], p[2], o[2], sfree[2];
 };
 
+template <bool HALF2>
 __global__ void __launch_bounds__(N_THREADS, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, AttnPrefillArgs a, uint32_t idesc_qk,
@@ -237,6 +246,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const float sc = 0.125f * LOG2E;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
+    // O of earlier tiles was accumulated against the old reference maximum: rescale it in TMEM
+    auto rescale_o = [&](float alpha) {
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t oreg[32];
+        tmem_ld_32x32(t_o + c * 32, oreg);
+        tmem_wait_ld_dep(oreg);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+        tmem_st_32x32(t_o + c * 32, oreg);
+      }
+      tmem_wait_st();
+    };
     for (int j = 0; j < n_mine; ++j) {
       if (ok && !mbar_wait_bounded(B.s[grp], j & 1)) {
         arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
@@ -247,95 +269,172 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       tc_fence_after();
       const int n_valid = min(max(my_cnt - j * BKV, 0), BKV);   // visible keys of this row in the tile
       const bool full = __all_sync(0xffffffffu, n_valid == BKV);
-      // the row's 128 scores, read once
-      uint32_t sv[4][32];
-      tmem_ld_32x32(t_s, sv[0]);
-      tmem_ld_32x32(t_s + 32, sv[1]);
-      tmem_ld_32x32(t_s + 64, sv[2]);
-      tmem_ld_32x32(t_s + 96, sv[3]);
-      tmem_wait_ld_dep(sv[0]);
-      tmem_wait_ld_dep(sv[1]);
-      tmem_wait_ld_dep(sv[2]);
-      tmem_wait_ld_dep(sv[3]);
-      // S is in registers: the tensor core may overwrite it with the next tile's scores
-      tc_fence_before();
-      mbar_arrive(B.sfree[grp]);
-      // row maximum of the visible raw scores (four independent chains)
-      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if constexpr (HALF2) {
+        // ---- packed-half path: scores are packed to half2 as they leave TMEM; max, scale-and-shift,
+        // exp2 (two per special-function instruction) and the row sum run on half2 ----
+        __half2 h2[64];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        if (full) {
-#pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            mx4[0] = fmaxf(mx4[0], __uint_as_float(sv[c][i]));
-            mx4[1] = fmaxf(mx4[1], __uint_as_float(sv[c][i + 1]));
-            mx4[2] = fmaxf(mx4[2], __uint_as_float(sv[c][i + 2]));
-            mx4[3] = fmaxf(mx4[3], __uint_as_float(sv[c][i + 3]));
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < n_valid) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
-        }
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
-      // raise the reference maximum only when it is far below the true one
-      float alpha = 1.f;
-      if (mx > m_ref + RESCALE_THRESHOLD) {  // also the first visible tile (m_ref = -inf)
-        alpha = (m_ref == -INFINITY) ? 0.f : ex2_fast(m_ref - mx);
-        m_ref = mx;
-      }
-      l *= alpha;
-      if (j > 0) {
-        // PV(j-1) must have retired: it reads the P buffer written below and updates O
-        bool good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
-        if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-        ok = __all_sync(0xffffffffu, good);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
-        // O of earlier tiles was accumulated against the old reference: rescale it in TMEM
-#pragma unroll
-        for (int c = 0; c < HD / 32; ++c) {
-          uint32_t oreg[32];
-          tmem_ld_32x32(t_o + c * 32, oreg);
-          tmem_wait_ld_dep(oreg);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
-          tmem_st_32x32(t_o + c * 32, oreg);
-        }
-        tmem_wait_st();
-      }
-      const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float ls0 = 0.f, ls1 = 0.f;
-      // probabilities -> shared memory (swizzled K-major, 16-bit)
-#pragma unroll
-      for (int c = 0; c < BKV / 32; ++c) {
-        uint32_t pk[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = ex2_fast(fmaf(__uint_as_float(sv[c][i]), sc, -m_safe));
-          float p1 = ex2_fast(fmaf(__uint_as_float(sv[c][i + 1]), sc, -m_safe));
+        for (int cc = 0; cc < 2; ++cc) {
+          uint32_t s0[32], s1[32];
+          tmem_ld_32x32(t_s + cc * 64, s0);
+          tmem_ld_32x32(t_s + cc * 64 + 32, s1);
+          tmem_wait_ld_dep(s0);
+          tmem_wait_ld_dep(s1);
           if (!full) {
-            if (c * 32 + i >= n_valid) p0 = 0.f;
-            if (c * 32 + i + 1 >= n_valid) p1 = 0.f;
-          }
-          ls0 += p0;
-          ls1 += p1;
-          pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
-        }
-        // columns [c*32, c*32+32) of row r: tile = c / 2, 16-byte chunks ch0 .. ch0+3
-        uint8_t* tile = p_row + (c >> 1) * (BQ * 128);
-        const int ch0 = (c & 1) * 4;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const int ch = (ch0 + q4) ^ (r & 7);
-          *reinterpret_cast<uint4*>(tile + ch * 16) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+            for (int i = 0; i < 32; ++i) {
+              if (cc * 64 + i >= n_valid) s0[i] = 0xff800000u;       // -inf: exp2 gives exactly 0
+              if (cc * 64 + 32 + i >= n_valid) s1[i] = 0xff800000u;
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            h2[cc * 32 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+            h2[cc * 32 + 16 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+          }
         }
+        // S is in registers: the tensor core may overwrite it with the next tile's scores
+        tc_fence_before();
+        mbar_arrive(B.sfree[grp]);
+        __half2 mx2[4] = {h2[0], h2[1], h2[2], h2[3]};
+#pragma unroll
+        for (int i = 4; i < 64; i += 4) {
+          mx2[0] = __hmax2(mx2[0], h2[i]);
+          mx2[1] = __hmax2(mx2[1], h2[i + 1]);
+          mx2[2] = __hmax2(mx2[2], h2[i + 2]);
+          mx2[3] = __hmax2(mx2[3], h2[i + 3]);
+        }
+        const __half2 mxx = __hmax2(__hmax2(mx2[0], mx2[1]), __hmax2(mx2[2], mx2[3]));
+        const float mx = fmaxf(__low2float(mxx), __high2float(mxx)) * sc;
+        float alpha = 1.f;
+        if (mx > m_ref + RESCALE_THRESHOLD) {  // also the first visible tile (m_ref = -inf)
+          const float m_new = __half2float(__float2half_rn(mx));  // the value the half2 math will use
+          alpha = (m_ref == -INFINITY) ? 0.f : ex2_fast(m_ref - m_new);
+          m_ref = m_new;
+        }
+        l *= alpha;
+        if (j > 0) {
+          // PV(j-1) must have retired: it reads the P buffer written below and updates O
+          bool good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
+          if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+          ok = __all_sync(0xffffffffu, good);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) rescale_o(alpha);
+        const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
+        const __half2 sc2 = __float2half2_rn(sc), nm2 = __float2half2_rn(-m_safe);
+        float lsum = 0.f;
+#pragma unroll
+        for (int g = 0; g < 8; ++g) {  // 8 half2 = 16 columns = two 16-byte chunks of the P row
+          __half2 p[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) p[e] = ex2_half2(__hfma2(h2[g * 8 + e], sc2, nm2));
+          const __half2 t = __hadd2(__hadd2(__hadd2(p[0], p[1]), __hadd2(p[2], p[3])),
+                                    __hadd2(__hadd2(p[4], p[5]), __hadd2(p[6], p[7])));
+          lsum += __low2float(t) + __high2float(t);
+          // columns [16 g, 16 g + 16): P sub-tile g / 4, chunks 2 (g % 4) and 2 (g % 4) + 1
+          uint8_t* tile = p_row + (g >> 2) * (BQ * 128);
+          const int ch0 = (g & 3) * 2;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int ch = (ch0 + q) ^ (r & 7);
+            *reinterpret_cast<uint4*>(tile + ch * 16) =
+                make_uint4(h2_bits(p[4 * q]), h2_bits(p[4 * q + 1]), h2_bits(p[4 * q + 2]), h2_bits(p[4 * q + 3]));
+          }
+        }
+        l += lsum;
+      } else {
+        // the row's 128 scores, read once
+        uint32_t sv[4][32];
+        tmem_ld_32x32(t_s, sv[0]);
+        tmem_ld_32x32(t_s + 32, sv[1]);
+        tmem_ld_32x32(t_s + 64, sv[2]);
+        tmem_ld_32x32(t_s + 96, sv[3]);
+        tmem_wait_ld_dep(sv[0]);
+        tmem_wait_ld_dep(sv[1]);
+        tmem_wait_ld_dep(sv[2]);
+        tmem_wait_ld_dep(sv[3]);
+        // S is in registers: the tensor core may overwrite it with the next tile's scores
+        tc_fence_before();
+        mbar_arrive(B.sfree[grp]);
+        // row maximum of the visible raw scores (four independent chains)
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  #pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (full) {
+  #pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+              mx4[0] = fmaxf(mx4[0], __uint_as_float(sv[c][i]));
+              mx4[1] = fmaxf(mx4[1], __uint_as_float(sv[c][i + 1]));
+              mx4[2] = fmaxf(mx4[2], __uint_as_float(sv[c][i + 2]));
+              mx4[3] = fmaxf(mx4[3], __uint_as_float(sv[c][i + 3]));
+            }
+          } else {
+  #pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i < n_valid) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sv[c][i]));
+          }
+        }
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+        // raise the reference maximum only when it is far below the true one
+        float alpha = 1.f;
+        if (mx > m_ref + RESCALE_THRESHOLD) {  // also the first visible tile (m_ref = -inf)
+          alpha = (m_ref == -INFINITY) ? 0.f : ex2_fast(m_ref - mx);
+          m_ref = mx;
+        }
+        l *= alpha;
+        if (j > 0) {
+          // PV(j-1) must have retired: it reads the P buffer written below and updates O
+          bool good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
+          if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+          ok = __all_sync(0xffffffffu, good);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+          // O of earlier tiles was accumulated against the old reference: rescale it in TMEM
+  #pragma unroll
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t oreg[32];
+            tmem_ld_32x32(t_o + c * 32, oreg);
+            tmem_wait_ld_dep(oreg);
+  #pragma unroll
+            for (int i = 0; i < 32; ++i) oreg[i] = __float_as_uint(__uint_as_float(oreg[i]) * alpha);
+            tmem_st_32x32(t_o + c * 32, oreg);
+          }
+          tmem_wait_st();
+        }
+        const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
+        float ls0 = 0.f, ls1 = 0.f;
+        // probabilities -> shared memory (swizzled K-major, 16-bit)
+  #pragma unroll
+        for (int c = 0; c < BKV / 32; ++c) {
+          uint32_t pk[16];
+  #pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float p0 = ex2_fast(fmaf(__uint_as_float(sv[c][i]), sc, -m_safe));
+            float p1 = ex2_fast(fmaf(__uint_as_float(sv[c][i + 1]), sc, -m_safe));
+            if (!full) {
+              if (c * 32 + i >= n_valid) p0 = 0.f;
+              if (c * 32 + i + 1 >= n_valid) p1 = 0.f;
+            }
+            ls0 += p0;
+            ls1 += p1;
+            pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
+          }
+          // columns [c*32, c*32+32) of row r: tile = c / 2, 16-byte chunks ch0 .. ch0+3
+          uint8_t* tile = p_row + (c >> 1) * (BQ * 128);
+          const int ch0 = (c & 1) * 4;
+  #pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const int ch = (ch0 + q4) ^ (r & 7);
+            *reinterpret_cast<uint4*>(tile + ch * 16) =
+                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+          }
+        }
+        l += ls0 + ls1;
       }
-      l += ls0 + ls1;
       // make the generic-proxy writes of P visible to the tensor-core (async) proxy
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
@@ -386,7 +485,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 bool arcb_attn_prefill_available() { return true; }
 
 int arcb_attn_prefill_init() {
-  return (int)cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  if (e != cudaSuccess) return (int)e;
+  return (int)cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
 }
 
 int arcb_launch_attn_prefill(const AttnPrefillArgs& a, cudaStream_t stream) {
@@ -404,7 +505,8 @@ int arcb_launch_attn_prefill(const AttnPrefillArgs& a, cudaStream_t stream) {
   const uint32_t idesc_qk = umma_idesc_f16(BQ, BKV, fmt, fmt, 0, 0);
   const uint32_t idesc_pv = umma_idesc_f16(BQ, HD, fmt, fmt, 0, 1);  // B = V is MN-major
   dim3 grid(a.n_qblocks, a.n_heads);
-  attn_prefill_kernel<<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv);
+  if (a.act_f16) attn_prefill_kernel<true><<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv);
+  else attn_prefill_kernel<false><<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv);
   arcb_count_launch(1);
   return (int)cudaGetLastError();
 }
