@@ -118,6 +118,74 @@ __device__ __forceinline__ void epi_qkv_quad(const GemmEpilogue& e, const RopeRo
   }
 }
 
+// Rotate the 16 rotary pairs [P0, P0 + 16) held in v[0..32) (P0 is 0 or 16: first or second half of
+// a 64-wide head).  Which table a pair uses (x: pairs 0-9, y: 10-19, z: 20-31) is known at compile
+// time, so the loop unrolls into straight table loads.
+template <int P0>
+__device__ __forceinline__ void rope_rotate32(const GemmEpilogue& e, const RopeRow& r, float (&v)[32]) {
+  const int nx = e.max_x * ARCB_ROPE_PX, ny = e.max_y * ARCB_ROPE_PY, nz = e.max_z * ARCB_ROPE_PZ;
+  const float* cx = e.rope + r.x * ARCB_ROPE_PX;
+  const float* sx = cx + nx;
+  const float* cy = e.rope + 2 * nx + r.y * ARCB_ROPE_PY;
+  const float* sy = cy + ny;
+  const float* cz = e.rope + 2 * nx + 2 * ny + r.z * ARCB_ROPE_PZ;
+  const float* sz = cz + nz;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    constexpr int PX = ARCB_ROPE_PX, PXY = ARCB_ROPE_PX + ARCB_ROPE_PY;
+    const int p = P0 + i;
+    float c, s;
+    if (p < PX) { c = __ldg(cx + p); s = __ldg(sx + p); }
+    else if (p < PXY) { c = __ldg(cy + (p - PX)); s = __ldg(sy + (p - PX)); }
+    else { c = __ldg(cz + (p - PXY)); s = __ldg(sz + (p - PXY)); }
+    const float a = v[2 * i], b = v[2 * i + 1];
+    v[2 * i] = a * c - b * s;
+    v[2 * i + 1] = b * c + a * s;
+  }
+}
+
+// 32 consecutive QKV output columns [n0, n0 + 32) of row m (n0 % 32 == 0: one half of one head of
+// one of the q / k / v sections): RoPE on q and k, then 16-byte stores of q16 or of the bf16 cache
+// row (+ the call's 16-bit K/V scratch row).
+__device__ __forceinline__ void epi_qkv_chunk32(const GemmEpilogue& e, const RopeRow& r, int m, int n0,
+                                                const uint32_t (&acc)[32]) {
+  const int d = e.d_model;
+  const int sec = n0 / d;
+  const int c = n0 - sec * d;
+  const int h = c >> 6, dim0 = c & 63;
+  float v[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+  if (sec < 2) {
+    if (dim0 == 0) rope_rotate32<0>(e, r, v);
+    else rope_rotate32<16>(e, r, v);
+  }
+  if (sec == 0) {
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.out16) + (size_t)m * d + c);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      dst[q] = make_uint4(pack2_act(v[8 * q], v[8 * q + 1], e.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], e.act_f16),
+                          pack2_act(v[8 * q + 4], v[8 * q + 5], e.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], e.act_f16));
+    return;
+  }
+  if (r.kv_row >= 0) {
+    __nv_bfloat16* base = (sec == 1) ? e.kcache : e.vcache;
+    uint4* dst = reinterpret_cast<uint4*>(base + (r.kv_row + (long long)h * e.t_max) * ARCB_HEAD_DIM + dim0);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      dst[q] = make_uint4(pack2_bf16(v[8 * q], v[8 * q + 1]), pack2_bf16(v[8 * q + 2], v[8 * q + 3]),
+                          pack2_bf16(v[8 * q + 4], v[8 * q + 5]), pack2_bf16(v[8 * q + 6], v[8 * q + 7]));
+  }
+  if (r.row16 >= 0) {
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>((sec == 1) ? e.k16 : e.v16) +
+                                          (size_t)r.row16 * d + c);
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+      dst[q] = make_uint4(pack2_act(v[8 * q], v[8 * q + 1], e.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], e.act_f16),
+                          pack2_act(v[8 * q + 4], v[8 * q + 5], e.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], e.act_f16));
+  }
+}
+
 __device__ __forceinline__ void epi_resid_quad(const GemmEpilogue& e, int m, int n, float4 v) {
   float4* px = reinterpret_cast<float4*>(e.x + (size_t)m * e.N + n);
   float4 r = *px;

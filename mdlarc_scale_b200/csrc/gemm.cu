@@ -194,14 +194,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_wait_ld();
           if (row_ok) {
+            if constexpr (MODE == EPI_QKV_ROPE) {
+              epi_qkv_chunk32(ep, rr, m, n0, r);
+            } else {
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                           __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-              const int n = n0 + 4 * q;
-              if constexpr (MODE == EPI_QKV_ROPE) epi_qkv_quad(ep, rr, m, n, v);
-              else if constexpr (MODE == EPI_RESID) epi_resid_quad(ep, m, n, v);
-              else epi_store_quad(ep, m, n, v);
+              for (int q = 0; q < 8; ++q) {
+                const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                             __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                const int n = n0 + 4 * q;
+                if constexpr (MODE == EPI_RESID) epi_resid_quad(ep, m, n, v);
+                else epi_store_quad(ep, m, n, v);
+              }
             }
           }
         }
