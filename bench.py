@@ -389,7 +389,7 @@ def run_ours(args, rank, world, local_rank):
                          "algorithmic_bytes_per_launch": attn_bytes},
             "prefill": {"tokens_per_s_per_gpu": prefill_tok_s, "tokens_per_step": prefill_tokens // args.steps},
         }
-        if not args.no_cpu and world >= 1:
+        if not args.no_cpu and world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
             v, cdt = cpu_generate_sample(args.cpu_seqs, args.cpu_steps, 777)
             line["cpu_baseline"] = {
