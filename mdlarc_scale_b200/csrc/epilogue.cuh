@@ -201,7 +201,7 @@ __device__ __forceinline__ void epi_store_quad(const GemmEpilogue& e, int m, int
   *reinterpret_cast<float4*>(e.y + (size_t)m * e.N + n) = v;
 }
 
-__device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.f + __expf(-g)); }
 
 // Packed column n (n % 128 < 64) holds gate outputs, n + 64 the matching up outputs.
 __device__ __forceinline__ void epi_swiglu_quad(const GemmEpilogue& e, int m, int n, float4 g,

@@ -4,7 +4,7 @@
 //   gemm_tc_kernel   : persistent; tcgen05.mma (UMMA 128x256x16 or 128x128x16), two fp32
 //                      accumulators in TMEM (the epilogue drains one while the next tile fills the
 //                      other), operands staged by TMA (128-byte swizzle) through an mbarrier ring;
-//                      warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-5 = epilogue.
+//                      warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = epilogue.
 //   gemm_simt_kernel : CUDA-core tile kernel for skinny M (weight streaming) and as
 //                      the cross-check of the tensor-core path.
 #include "gemm.cuh"
@@ -19,6 +19,8 @@ namespace {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;  // 64 x 2 B = one 128-byte swizzle row
+constexpr int TC_EPI_WARPS = 8;                  // two warps per TMEM lane quarter, half of the columns each
+constexpr int TC_THREADS = 64 + 32 * TC_EPI_WARPS;
 
 template <int BN>
 struct TcCfg {
@@ -35,7 +37,7 @@ struct TcCfg {
 // running at the same time share A rows through L2).  The TMA->MMA shared-memory ring runs
 // continuously across tiles; accumulators alternate between two TMEM buffers.
 template <int BN, int MODE>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                GemmEpilogue ep, int K, uint32_t idesc, int tiles_n, int tiles_total) {
   using Cfg = TcCfg<BN>;
@@ -61,7 +63,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(bar_acc_full + 8 * b, 1);
-      mbar_init(bar_acc_empty + 8 * b, 128);
+      mbar_init(bar_acc_empty + 8 * b, 32 * TC_EPI_WARPS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -141,8 +143,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     }
   } else {
-    // ---- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----
+    // ---- epilogue: warps 2..9, TMEM lane quarter = warp % 4, column half = (warp - 2) / 4 ----
     const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
     uint32_t it = 0;
     for (int tile = blockIdx.x; tile < tiles_total; tile += gridDim.x, ++it) {
@@ -163,11 +166,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (MODE == EPI_QKV_ROPE && row_ok) rr = rope_row_ctx(ep, m);
       if constexpr (MODE == EPI_SWIGLU) {
         // gate columns [0,64) and up columns [64,128) of every 128-column group
+        // BN = 256: each column half owns one 128-column group; BN = 128: one 32-column pair each
+        const int g_begin = (BN == 256) ? col_half * 128 : 0, g_end = (BN == 256) ? g_begin + 128 : 128;
+        const int c_begin = (BN == 256) ? 0 : col_half, c_end = (BN == 256) ? 2 : col_half + 1;
 #pragma unroll 1
-        for (int g0 = 0; g0 < BN; g0 += 128) {
+        for (int g0 = g_begin; g0 < g_end; g0 += 128) {
           if (n_blk * BN + g0 >= ep.N) break;  // warp-uniform: tile tail beyond N
 #pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
+          for (int c = c_begin; c < c_end; ++c) {
             uint32_t rg[32], ru[32];
             tmem_ld_32x32(t_row + g0 + c * 32, rg);
             tmem_ld_32x32(t_row + g0 + 64 + c * 32, ru);
@@ -187,7 +193,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
       } else {
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
+        for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
           const int n0 = n_blk * BN + c * 32;
           if (n0 >= ep.N) break;  // warp-uniform
           uint32_t r[32];
@@ -377,7 +383,7 @@ static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEp
   const int tiles = tiles_n * tiles_m;
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
   const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
-  gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, 192, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc,
+  gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, TC_THREADS, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc,
                                                                                             tiles_n, tiles);
 }
 
