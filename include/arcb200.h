@@ -37,6 +37,8 @@ extern "C" {
 #define ARCB_GEMM_AUTO 0 /* tcgen05 GEMM when M > 32, weight-streaming below   */
 #define ARCB_GEMM_SIMT 1 /* CUDA-core GEMM everywhere (debug cross-check)      */
 #define ARCB_GEMM_TC 2   /* tcgen05 GEMM everywhere                            */
+#define ARCB_GEMM_TC_1CTA 3 /* arcb_op_gemm only: the 1-CTA tcgen05 kernels        */
+#define ARCB_GEMM_TC_2CTA 4 /* arcb_op_gemm only: the 2-CTA (cta_group::2) kernel  */
 
 #define ARCB_ATTN_AUTO 0   /* tcgen05 flash prefill when available             */
 #define ARCB_ATTN_STREAM 1 /* per-query streaming kernel for prefill as well   */

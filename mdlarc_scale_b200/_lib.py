@@ -10,7 +10,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "libarcb200.so"
 
 ACT_F16, ACT_BF16 = 0, 1
-GEMM_AUTO, GEMM_SIMT, GEMM_TC = 0, 1, 2
+GEMM_AUTO, GEMM_SIMT, GEMM_TC, GEMM_TC_1CTA, GEMM_TC_2CTA = 0, 1, 2, 3, 4
 ATTN_AUTO, ATTN_STREAM = 0, 1
 
 E_ARG, E_STATE, E_DEVICE, E_UNSUPPORTED = -1, -2, -3, -4

@@ -547,14 +547,15 @@ extern "C" int arcb_op_gemm(const void* a16, const void* w, float* y, int32_t M,
   static bool inited = false;
   if (!inited) { CKL(arcb_gemm_init(), "gemm init"); inited = true; }
   if (N % 128 || K % 32) return fail(ARCB_E_ARG, "gemm needs N % 128 == 0 and K % 32 == 0");
-  bool tc = gemm_path == ARCB_GEMM_TC || (gemm_path == ARCB_GEMM_AUTO && M > 32);
+  const int variant = gemm_path == ARCB_GEMM_TC_1CTA ? 1 : (gemm_path == ARCB_GEMM_TC_2CTA ? 2 : 0);
+  bool tc = gemm_path == ARCB_GEMM_TC || variant != 0 || (gemm_path == ARCB_GEMM_AUTO && M > 32);
   if (tc && !arcb_gemm_tc_supported(M, N, K)) {
-    if (gemm_path == ARCB_GEMM_TC) return fail(ARCB_E_ARG, "tcgen05 gemm needs K % 64 == 0");
+    if (gemm_path != ARCB_GEMM_AUTO) return fail(ARCB_E_ARG, "tcgen05 gemm needs K % 64 == 0");
     tc = false;
   }
   GemmEpilogue ep{};
   ep.mode = EPI_STORE_F32; ep.M = M; ep.N = N; ep.y = y;
-  CKL(arcb_launch_gemm(a16, w, ep, K, act_format == ARCB_ACT_F16, tc, (cudaStream_t)stream), "gemm");
+  CKL(arcb_launch_gemm(a16, w, ep, K, act_format == ARCB_ACT_F16, tc, (cudaStream_t)stream, variant), "gemm");
   return ARCB_OK;
 }
 

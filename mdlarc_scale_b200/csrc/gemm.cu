@@ -33,6 +33,71 @@ struct TcCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+// Drains one accumulator tile (this thread's row, the 32-column chunks of its column half) from
+// TMEM through the epilogue MODE.  t_row: TMEM address of the row's first accumulator column;
+// n_tile0: first output column of the tile.  tcgen05.ld is warp-collective, so every lane runs the
+// loads and only the stores are predicated on row_ok.
+template <int BN, int MODE>
+__device__ __forceinline__ void epilogue_tile(const GemmEpilogue& ep, uint32_t t_row, int m, bool row_ok,
+                                              int n_tile0, int col_half) {
+  RopeRow rr;
+  rr.x = rr.y = rr.z = 0;
+  rr.kv_row = -1;
+  rr.row16 = -1;
+  if (MODE == EPI_QKV_ROPE && row_ok) rr = rope_row_ctx(ep, m);
+  if constexpr (MODE == EPI_SWIGLU) {
+    // gate columns [0,64) and up columns [64,128) of every 128-column group
+    // BN = 256: each column half owns one 128-column group; BN = 128: one 32-column pair each
+    const int g_begin = (BN == 256) ? col_half * 128 : 0, g_end = (BN == 256) ? g_begin + 128 : 128;
+    const int c_begin = (BN == 256) ? 0 : col_half, c_end = (BN == 256) ? 2 : col_half + 1;
+#pragma unroll 1
+    for (int g0 = g_begin; g0 < g_end; g0 += 128) {
+      if (n_tile0 + g0 >= ep.N) break;  // warp-uniform: tile tail beyond N
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; ++c) {
+        uint32_t rg[32], ru[32];
+        tmem_ld_32x32(t_row + g0 + c * 32, rg);
+        tmem_ld_32x32(t_row + g0 + 64 + c * 32, ru);
+        tmem_wait_ld();
+        if (row_ok) {
+          const int n0 = n_tile0 + g0 + c * 32;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 g = make_float4(__uint_as_float(rg[4 * q]), __uint_as_float(rg[4 * q + 1]),
+                                         __uint_as_float(rg[4 * q + 2]), __uint_as_float(rg[4 * q + 3]));
+            const float4 u = make_float4(__uint_as_float(ru[4 * q]), __uint_as_float(ru[4 * q + 1]),
+                                         __uint_as_float(ru[4 * q + 2]), __uint_as_float(ru[4 * q + 3]));
+            epi_swiglu_quad(ep, m, n0 + 4 * q, g, u);
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
+      const int n0 = n_tile0 + c * 32;
+      if (n0 >= ep.N) break;  // warp-uniform
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c * 32, r);
+      tmem_wait_ld();
+      if (row_ok) {
+        if constexpr (MODE == EPI_QKV_ROPE) {
+          epi_qkv_chunk32(ep, rr, m, n0, r);
+        } else {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                         __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+            const int n = n0 + 4 * q;
+            if constexpr (MODE == EPI_RESID) epi_resid_quad(ep, m, n, v);
+            else epi_store_quad(ep, m, n, v);
+          }
+        }
+      }
+    }
+  }
+}
+
 // Persistent kernel: CTA c processes output tiles c, c + gridDim.x, ... (n fastest, so the CTAs
 // running at the same time share A rows through L2).  The TMA->MMA shared-memory ring runs
 // continuously across tiles; accumulators alternate between two TMEM buffers.
@@ -159,62 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-      RopeRow rr;
-      rr.x = rr.y = rr.z = 0;
-      rr.kv_row = -1;
-      rr.row16 = -1;
-      if (MODE == EPI_QKV_ROPE && row_ok) rr = rope_row_ctx(ep, m);
-      if constexpr (MODE == EPI_SWIGLU) {
-        // gate columns [0,64) and up columns [64,128) of every 128-column group
-        // BN = 256: each column half owns one 128-column group; BN = 128: one 32-column pair each
-        const int g_begin = (BN == 256) ? col_half * 128 : 0, g_end = (BN == 256) ? g_begin + 128 : 128;
-        const int c_begin = (BN == 256) ? 0 : col_half, c_end = (BN == 256) ? 2 : col_half + 1;
-#pragma unroll 1
-        for (int g0 = g_begin; g0 < g_end; g0 += 128) {
-          if (n_blk * BN + g0 >= ep.N) break;  // warp-uniform: tile tail beyond N
-#pragma unroll 1
-          for (int c = c_begin; c < c_end; ++c) {
-            uint32_t rg[32], ru[32];
-            tmem_ld_32x32(t_row + g0 + c * 32, rg);
-            tmem_ld_32x32(t_row + g0 + 64 + c * 32, ru);
-            tmem_wait_ld();
-            if (row_ok) {
-              const int n0 = n_blk * BN + g0 + c * 32;
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 g = make_float4(__uint_as_float(rg[4 * q]), __uint_as_float(rg[4 * q + 1]),
-                                             __uint_as_float(rg[4 * q + 2]), __uint_as_float(rg[4 * q + 3]));
-                const float4 u = make_float4(__uint_as_float(ru[4 * q]), __uint_as_float(ru[4 * q + 1]),
-                                             __uint_as_float(ru[4 * q + 2]), __uint_as_float(ru[4 * q + 3]));
-                epi_swiglu_quad(ep, m, n0 + 4 * q, g, u);
-              }
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
-          const int n0 = n_blk * BN + c * 32;
-          if (n0 >= ep.N) break;  // warp-uniform
-          uint32_t r[32];
-          tmem_ld_32x32(t_row + c * 32, r);
-          tmem_wait_ld();
-          if (row_ok) {
-            if constexpr (MODE == EPI_QKV_ROPE) {
-              epi_qkv_chunk32(ep, rr, m, n0, r);
-            } else {
-#pragma unroll
-              for (int q = 0; q < 8; ++q) {
-                const float4 v = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                                             __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
-                const int n = n0 + 4 * q;
-                if constexpr (MODE == EPI_RESID) epi_resid_quad(ep, m, n, v);
-                else epi_store_quad(ep, m, n, v);
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained: hand it back to the MMA warp
       tc_fence_before();
       mbar_arrive(bar_acc_empty + 8 * acc);
@@ -225,6 +235,166 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 2-CTA tcgen05 kernel (cta_group::2): a cluster of two CTAs owns one 256 x 256 output tile.
+// CTA r of the pair loads its 128 rows of A and its 128 rows of W (each operand slice crosses
+// L2 -> shared memory once per pair, no multicast), CTA 0 issues one 256 x 256 x 16 MMA that reads
+// both CTAs' shared memory and writes 128 x 256 accumulators into each CTA's TMEM, and every CTA
+// runs the epilogue of its own 128 rows.  Per SM this halves the shared-memory traffic per FLOP
+// of the 1-CTA 128 x 256 tile, which is what bounds that kernel.
+// Barriers: full[s] lives in CTA 0 (both CTAs' TMA loads complete on it); empty[s] and acc_full[b]
+// are signalled in both CTAs by a multicast commit; acc_empty[b] of CTA 0 collects one arrival
+// per epilogue warp of both CTAs.
+// ---------------------------------------------------------------------------
+struct Tc2Cfg {
+  static constexpr int BN = 256;
+  static constexpr int STAGES = 6;
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;   // this CTA's 128 rows of A
+  static constexpr int B_BYTES = 128 * TC_BK * 2;     // this CTA's 128 rows of W
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 2 * BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                GemmEpilogue ep, int K, uint32_t idesc, int tiles_n, int tiles_total) {
+  using Cfg = Tc2Cfg;
+  constexpr int BN = Cfg::BN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t bar_base = base + Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_acc_full = bar_base + 16 * Cfg::STAGES;
+  const uint32_t bar_acc_empty = bar_acc_full + 16;
+  volatile uint32_t* tmem_slot =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 16 * Cfg::STAGES + 32);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();       // 0 = leader (issues the MMAs)
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int num_k = K / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(bar_base + 8 * s, 1);                   // full: one expect_tx arrival (CTA 0's producer)
+      mbar_init(bar_base + 8 * (Cfg::STAGES + s), 1);   // empty: one multicast commit
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_acc_full + 8 * b, 1);
+      mbar_init(bar_acc_empty + 8 * b, 2 * TC_EPI_WARPS);  // one arrival per epilogue warp of both CTAs
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    tmem_relinquish_2cta();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive / TMA completion
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---- TMA producer (both CTAs) ----
+    if (lane == 0) {
+      uint32_t kbt = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < tiles_total; tile += n_pairs) {
+        const int m_blk = tile / tiles_n, n_blk = tile - m_blk * tiles_n;
+        for (int kb = 0; kb < num_k; ++kb, ++kbt) {
+          const int s = kbt % Cfg::STAGES;
+          const uint32_t ph = (kbt / Cfg::STAGES) & 1;
+          if (!mbar_wait_bounded(bar_base + 8 * (Cfg::STAGES + s), ph ^ 1)) {
+            arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_MMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          if (*abort_flag) { ok = false; break; }
+          const uint32_t full = bar_base + 8 * s;
+          const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
+          if (rank == 0) mbar_expect_tx(full, 2 * Cfg::STAGE_BYTES);  // both CTAs' bytes land on CTA 0's barrier
+          tma_load_2d_2cta(a_dst, &tmap_a, kb * TC_BK, m_blk * 256 + (int)rank * 128, full);
+          tma_load_2d_2cta(a_dst + Cfg::A_BYTES, &tmap_b, kb * TC_BK, n_blk * BN + (int)rank * 128, full);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer (leader CTA only) ----
+    if (lane == 0 && rank == 0) {
+      uint32_t kbt = 0, it = 0;
+      bool ok = true;
+      for (int tile = pair; ok && tile < tiles_total; tile += n_pairs, ++it) {
+        const uint32_t acc = it & 1;
+        if (!mbar_wait_bounded(bar_acc_empty + 8 * acc, ((it >> 1) & 1) ^ 1)) {
+          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb, ++kbt) {
+          const int s = kbt % Cfg::STAGES;
+          const uint32_t ph = (kbt / Cfg::STAGES) & 1;
+          if (!mbar_wait_bounded(bar_base + 8 * s, ph)) {
+            arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = base + s * Cfg::STAGE_BYTES;
+          const uint64_t da = umma_desc_k_sw128(a_addr);
+          const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+#pragma unroll
+          for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+            umma_f16_2cta(d_tmem, da + 2 * k4, db + 2 * k4, idesc, (kb | k4) ? 1u : 0u);
+          umma_commit_2cta(bar_base + 8 * (Cfg::STAGES + s));  // frees the stage in both CTAs
+        }
+        if (ok) umma_commit_2cta(bar_acc_full + 8 * acc);
+      }
+    }
+  } else {
+    // ---- epilogue (both CTAs): warps 2..9, TMEM lane quarter = warp % 4, column half = (warp - 2) / 4 ----
+    const int quarter = warp & 3;
+    const int col_half = (warp - 2) >> 2;
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t it = 0;
+    for (int tile = pair; tile < tiles_total; tile += n_pairs, ++it) {
+      const int m_blk = tile / tiles_n, n_blk = tile - m_blk * tiles_n;
+      const uint32_t acc = it & 1;
+      const int m = m_blk * 256 + (int)rank * 128 + row_in_tile;
+      const bool row_ok = m < ep.M;
+      bool ok = mbar_wait_bounded(bar_acc_full + 8 * acc, (it >> 1) & 1);
+      if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
+      // accumulator drained by this warp: tell the leader's MMA thread
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cta0(bar_acc_empty + 8 * acc);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA leaves (or frees TMEM) while the pair's MMAs may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_2cta(tmem_base, Cfg::TMEM_COLS);
   }
 }
 
@@ -361,6 +531,12 @@ static cudaError_t set_tc_smem_attr() {
 }
 
 static int g_num_sms = 0;
+static int g_max_pairs = 0;  // 2-CTA clusters that can be resident at once
+
+template <int MODE>
+static cudaError_t set_tc2_smem_attr() {
+  return cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Cfg::SMEM_BYTES);
+}
 
 // Opt in to the large dynamic shared memory of every tcgen05 instantiation (call once, outside
 // any stream capture).
@@ -370,6 +546,24 @@ int arcb_gemm_init() {
   if ((e = set_tc_smem_attr<EPI_QKV_ROPE>()) != cudaSuccess) return (int)e;
   if ((e = set_tc_smem_attr<EPI_RESID>()) != cudaSuccess) return (int)e;
   if ((e = set_tc_smem_attr<EPI_SWIGLU>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc2_smem_attr<EPI_STORE_F32>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc2_smem_attr<EPI_QKV_ROPE>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc2_smem_attr<EPI_RESID>()) != cudaSuccess) return (int)e;
+  if ((e = set_tc2_smem_attr<EPI_SWIGLU>()) != cudaSuccess) return (int)e;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 148);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = Tc2Cfg::SMEM_BYTES;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<EPI_RESID>, &cfg) == cudaSuccess) g_max_pairs = n;
+    else cudaGetLastError();
+  }
   int dev = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
   if ((e = cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
@@ -388,20 +582,36 @@ static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEp
 }
 
 template <int MODE>
+static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue& ep, int K, int act_f16,
+                       cudaStream_t stream) {
+  const int tiles_n = (ep.N + 255) / 256, tiles_m = (ep.M + 255) / 256;
+  const int tiles = tiles_n * tiles_m;
+  const int pairs = tiles < g_max_pairs ? tiles : g_max_pairs;
+  const uint32_t idesc = umma_idesc_f16(256, 256, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
+  gemm_tc2_kernel<MODE><<<2 * pairs, TC_THREADS, Tc2Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc, tiles_n, tiles);
+}
+
+int arcb_gemm_max_pairs() { return g_max_pairs; }
+
+template <int MODE>
 static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue& ep, int K,
-                            int act_f16, bool use_tc, cudaStream_t stream) {
+                            int act_f16, bool use_tc, int tc_variant, cudaStream_t stream) {
   const int M = ep.M, N = ep.N;
   if (use_tc) {
     // 128 x 256 tiles (one CTA per SM, persistent) unless that leaves most SMs without a tile
     const int sms = g_num_sms > 0 ? g_num_sms : 148;
     const int tiles256 = ((N + 255) / 256) * ((M + TC_BM - 1) / TC_BM);
     const bool wide = tiles256 * 10 >= sms * 7;
+    // 256 x 256 tiles on CTA pairs when there are enough of them to occupy the machine
+    const int tiles2 = ((N + 255) / 256) * ((M + 255) / 256);
+    const bool pair = g_max_pairs > 0 && (tc_variant == 2 || (tc_variant == 0 && tiles2 * 10 >= g_max_pairs * 7));
     CUtensorMap ta, tb;
     int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
     if (r) return 1000 + r;
-    r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, wide ? 256 : 128, TC_BK, act_f16);
+    r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, (wide && !pair) ? 256 : 128, TC_BK, act_f16);
     if (r) return 1000 + r;
-    if (wide) launch_tc<256, MODE>(ta, tb, ep, K, act_f16, stream);
+    if (pair) launch_tc2<MODE>(ta, tb, ep, K, act_f16, stream);
+    else if (wide) launch_tc<256, MODE>(ta, tb, ep, K, act_f16, stream);
     else launch_tc<128, MODE>(ta, tb, ep, K, act_f16, stream);
   } else {
     dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
@@ -414,16 +624,16 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
 }
 
 int arcb_launch_gemm(const void* a16, const void* w16, const GemmEpilogue& ep, int K, int act_f16,
-                     bool use_tc, cudaStream_t stream) {
+                     bool use_tc, cudaStream_t stream, int tc_variant) {
   const int M = ep.M, N = ep.N;
   if (M <= 0) return 0;
   if (N % 128 != 0 || K % 32 != 0) return -1;
   if (use_tc && !arcb_gemm_tc_supported(M, N, K)) return -1;
   switch (ep.mode) {
-    case EPI_STORE_F32: return launch_gemm_mode<EPI_STORE_F32>(a16, w16, ep, K, act_f16, use_tc, stream);
-    case EPI_QKV_ROPE: return launch_gemm_mode<EPI_QKV_ROPE>(a16, w16, ep, K, act_f16, use_tc, stream);
-    case EPI_RESID: return launch_gemm_mode<EPI_RESID>(a16, w16, ep, K, act_f16, use_tc, stream);
-    case EPI_SWIGLU: return launch_gemm_mode<EPI_SWIGLU>(a16, w16, ep, K, act_f16, use_tc, stream);
+    case EPI_STORE_F32: return launch_gemm_mode<EPI_STORE_F32>(a16, w16, ep, K, act_f16, use_tc, tc_variant, stream);
+    case EPI_QKV_ROPE: return launch_gemm_mode<EPI_QKV_ROPE>(a16, w16, ep, K, act_f16, use_tc, tc_variant, stream);
+    case EPI_RESID: return launch_gemm_mode<EPI_RESID>(a16, w16, ep, K, act_f16, use_tc, tc_variant, stream);
+    case EPI_SWIGLU: return launch_gemm_mode<EPI_SWIGLU>(a16, w16, ep, K, act_f16, use_tc, tc_variant, stream);
   }
   return -1;
 }

@@ -30,7 +30,8 @@ def test_rmsnorm(lib, fmt, rows, d):
     assert torch.allclose(out.float(), ref, rtol=eps, atol=1e-4)
 
 
-@pytest.mark.parametrize("path", [_lib.GEMM_SIMT, _lib.GEMM_TC], ids=["simt", "tc"])
+@pytest.mark.parametrize("path", [_lib.GEMM_SIMT, _lib.GEMM_TC, _lib.GEMM_TC_1CTA, _lib.GEMM_TC_2CTA],
+                         ids=["simt", "tc", "tc1cta", "tc2cta"])
 @pytest.mark.parametrize("fmt", [_lib.ACT_BF16, _lib.ACT_F16], ids=["bf16", "f16"])
 @pytest.mark.parametrize("M,N,K", [(1, 128, 64), (8, 768, 256), (33, 256, 704), (128, 384, 128),
                                    (300, 1408, 256), (1000, 1280, 3392),
