@@ -20,7 +20,9 @@ import torch
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
 sys.path.insert(0, str(ROOT))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py /path/to/reference")
+REF = sys.argv[1]
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 
