@@ -127,6 +127,13 @@ typedef struct arcb_session_desc {
   int32_t* d_out_tokens;      /* int32 [B][max_new]: generated tokens                 */
   const int32_t* d_forced;    /* optional int32 [B][max_new]: teacher-forced tokens   */
   float* d_step_logits;       /* optional fp32 [B][max_new][14]: logits of every step */
+  /* Soft decoding constraints (_apply_logit_constraints, src/inference.py:285-364), applied to a
+   * copy of the logits before the argmax; all optional (NULL / 0 = off):                        */
+  const uint8_t* d_palette_mask; /* [B][10], 1 = colour allowed; disallowed colours lose palette_penalty */
+  const int32_t* d_target_shape; /* [B][2] (h, w), negative = no shape constraint for that row     */
+  float palette_penalty;
+  float shape_penalty;
+  uint32_t disallow_token_mask;  /* bit t set: token t gets -inf (reference default: START, IO_SEP) */
 } arcb_session_desc;
 
 int64_t arcb_session_workspace_bytes(const arcb_engine* eng, int32_t n_seqs,

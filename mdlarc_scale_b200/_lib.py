@@ -50,6 +50,8 @@ class SessionDesc(C.Structure):
         ("d_kv_cache", C.c_void_p), ("kv_cache_bytes", C.c_int64),
         ("d_workspace", C.c_void_p), ("workspace_bytes", C.c_int64),
         ("d_out_tokens", C.c_void_p), ("d_forced", C.c_void_p), ("d_step_logits", C.c_void_p),
+        ("d_palette_mask", C.c_void_p), ("d_target_shape", C.c_void_p),
+        ("palette_penalty", C.c_float), ("shape_penalty", C.c_float), ("disallow_token_mask", C.c_uint32),
     ]
 
 

@@ -329,6 +329,11 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
   st.out_tokens = dsc->d_out_tokens;
   st.forced = dsc->d_forced;
   st.step_logits = dsc->d_step_logits;
+  st.palette_mask = dsc->d_palette_mask;
+  st.target_shape = dsc->d_target_shape;
+  st.palette_penalty = dsc->palette_penalty;
+  st.shape_penalty = dsc->shape_penalty;
+  st.disallow_mask = dsc->disallow_token_mask & 0x3fffu;
   st.err = e->d_err;
   cudaError_t r = cudaMemset(ints, 0, w.n_int * 4);
   if (r != cudaSuccess) { delete s; return fail_cuda(r, "cudaMemset(session state)"); }

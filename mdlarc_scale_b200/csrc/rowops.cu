@@ -182,6 +182,41 @@ head_kernel(HeadArgs a, DecodeState st) {
     out_idx = st.cur_len[b] - st.len0[b] + 1;
     st.cur_len[b] = min(st.cur_len[b] + 1, st.t_max);
   }
+  // Soft constraints (src/inference.py:285-364) act on a copy of the logits, using the grid state
+  // after the last fed token (st.gx / st.gy were advanced by decode_begin, or armed just above).
+  if (st.disallow_mask || st.palette_mask || st.target_shape) {
+    float adj[ARCB_VOCAB];
+#pragma unroll
+    for (int v = 0; v < ARCB_VOCAB; ++v) adj[v] = ((st.disallow_mask >> v) & 1u) ? -INFINITY : acc[v];
+    if (st.palette_mask) {
+#pragma unroll
+      for (int c = 0; c < 10; ++c)
+        if (!st.palette_mask[(size_t)b * 10 + c]) adj[c] -= st.palette_penalty;
+    }
+    if (st.target_shape) {
+      const int th = st.target_shape[2 * b], tw = st.target_shape[2 * b + 1];
+      if (th >= 0 && tw >= 0) {
+        const int gx = st.gx[b], gy = st.gy[b];
+        const bool row_full = gx >= tw, past_end = gy >= th;
+        if (row_full) {
+#pragma unroll
+          for (int c = 0; c < 10; ++c) adj[c] -= st.shape_penalty;
+        } else {
+          adj[TOK_NEWLINE] -= st.shape_penalty;
+        }
+        if (past_end) {
+#pragma unroll
+          for (int c = 0; c < 10; ++c) adj[c] -= st.shape_penalty;
+          adj[TOK_NEWLINE] -= st.shape_penalty;
+        }
+      }
+    }
+    best = 0;
+    float bv2 = adj[0];
+#pragma unroll
+    for (int v = 1; v < ARCB_VOCAB; ++v)
+      if (adj[v] > bv2) { bv2 = adj[v]; best = v; }
+  }
   int tok = best;
   const bool in_range = out_idx >= 0 && out_idx < st.max_new;
   if (st.forced && in_range) tok = st.forced[(size_t)b * st.max_new + out_idx];

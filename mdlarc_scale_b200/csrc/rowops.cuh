@@ -16,7 +16,12 @@ struct DecodeState {
   int* n_finished;
   int* out_tokens;          // [B][max_new]
   const int* forced;        // optional [B][max_new]
-  float* step_logits;       // optional [B][max_new][14]
+  float* step_logits;       // optional [B][max_new][14] (raw logits, before constraints)
+  // soft decoding constraints (all optional)
+  const unsigned char* palette_mask;  // [B][10], 1 = allowed
+  const int* target_shape;            // [B][2] (h, w), negative = none
+  float palette_penalty, shape_penalty;
+  unsigned int disallow_mask;         // bit t: token t -> -inf
   int* err;
 };
 

@@ -145,9 +145,10 @@ class Engine:
 
     def new_session(self, n_seqs: int, t_max: int, max_new: int, max_prefill_tokens: int,
                     stop_on_end: bool = True, attn_splits: int = 0, forced: torch.Tensor | None = None,
-                    want_step_logits: bool = False, out_tokens: torch.Tensor | None = None) -> "Session":
+                    want_step_logits: bool = False, out_tokens: torch.Tensor | None = None,
+                    constraints: dict | None = None) -> "Session":
         return Session(self, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end, attn_splits,
-                       forced, want_step_logits, out_tokens)
+                       forced, want_step_logits, out_tokens, constraints)
 
 
 _ENGINES: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
@@ -173,7 +174,7 @@ class Session:
     """A static KV cache, the greedy-loop state and the decode graph for ``n_seqs`` sequences."""
 
     def __init__(self, eng: Engine, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end,
-                 attn_splits, forced, want_step_logits, out_tokens=None):
+                 attn_splits, forced, want_step_logits, out_tokens=None, constraints=None):
         self.eng = eng
         self.n_seqs, self.t_max, self.max_new = int(n_seqs), int(t_max), int(max_new)
         self.max_prefill_tokens = int(max_prefill_tokens)
@@ -199,6 +200,23 @@ class Session:
             assert self.forced.shape == (self.n_seqs, self.max_new)
         self.step_logits = (torch.zeros((self.n_seqs, self.max_new, VOCAB), dtype=torch.float32, device=dev)
                             if want_step_logits else None)
+        # soft decoding constraints: dict(palette_mask=[B,10] bool|None, target_shape=[B,2] int|None,
+        # palette_penalty, shape_penalty, disallow_tokens)
+        self.palette_mask = self.target_shape = None
+        pal_pen = shp_pen = 0.0
+        disallow = 0
+        if constraints is not None:
+            pm, ts = constraints.get("palette_mask"), constraints.get("target_shape")
+            if pm is not None:
+                self.palette_mask = torch.as_tensor(pm).to(device=dev, dtype=torch.uint8).contiguous()
+                assert tuple(self.palette_mask.shape) == (self.n_seqs, 10)
+            if ts is not None:
+                self.target_shape = torch.as_tensor(ts).to(device=dev, dtype=torch.int32).contiguous()
+                assert tuple(self.target_shape.shape) == (self.n_seqs, 2)
+            pal_pen = float(constraints.get("palette_penalty", 2.0))
+            shp_pen = float(constraints.get("shape_penalty", 2.0))
+            for t in constraints.get("disallow_tokens", ()):
+                disallow |= 1 << int(t)
         desc = _lib.SessionDesc(
             n_seqs=self.n_seqs, t_max=self.t_max, max_new=self.max_new,
             max_prefill_tokens=self.max_prefill_tokens, attn_splits=int(attn_splits),
@@ -206,7 +224,9 @@ class Session:
             d_kv_cache=self.kv_cache.data_ptr(), kv_cache_bytes=kv_bytes,
             d_workspace=self.workspace.data_ptr(), workspace_bytes=ws_bytes,
             d_out_tokens=self.out_tokens.data_ptr(), d_forced=_ptr(self.forced),
-            d_step_logits=_ptr(self.step_logits))
+            d_step_logits=_ptr(self.step_logits),
+            d_palette_mask=_ptr(self.palette_mask), d_target_shape=_ptr(self.target_shape),
+            palette_penalty=pal_pen, shape_penalty=shp_pen, disallow_token_mask=disallow)
         self._handle = C.c_void_p()
         with torch.cuda.device(dev):
             _lib.check(lib.arcb_session_create(eng._handle, C.byref(desc), C.byref(self._handle)))

@@ -1,8 +1,8 @@
 """Drop-in for the reference's generation API (``src/inference.py``) on the B200 engine.
 
 ``generate_output`` and ``predict_with_augmentations`` keep the reference's signatures, argument
-meaning and error behaviour; only greedy, unconstrained decoding is implemented natively
-(sampling and soft constraints raise ``NotImplementedError`` rather than falling back).
+meaning and error behaviour; greedy decoding, with or without the soft palette / shape constraints,
+is implemented natively (sampling raises ``NotImplementedError`` rather than falling back).
 
 Differences from the reference that are part of the design:
   * prompts are packed (no padded positions are computed) and the KV cache is compacted, which
@@ -28,12 +28,34 @@ POLL_EVERY = 32                 # decode steps between two host checks of the fi
 
 @dataclass(frozen=True)
 class DecodingConstraints:
-    """Placeholder with the reference's fields (src/inference.py:36-43); not implemented natively."""
-    palette_mask: torch.Tensor | None = None
-    target_shape: torch.Tensor | None = None
+    """Soft decoding constraints with the reference's fields (src/inference.py:36-43): applied on the
+    device, inside the kernel that picks the next token."""
+    palette_mask: torch.Tensor | None = None   # [batch, 10] bool, True = colour allowed
+    target_shape: torch.Tensor | None = None   # [batch, 2] (h, w), negative = no constraint
     palette_penalty: float = 2.0
     shape_penalty: float = 2.0
-    disallow_tokens: tuple = (10, 12)
+    disallow_tokens: tuple = (10, 12)          # START, IO_SEP
+
+
+def _constraints_dict(constraints, batch: int) -> dict | None:
+    """Host arrays for the session; batch broadcasting as in _apply_logit_constraints
+    (src/inference.py:298-347): [1, n] rows are expanded, any other mismatch drops that constraint."""
+    if constraints is None:
+        return None
+
+    def fit(t, width, dtype):
+        if t is None:
+            return None
+        arr = np.asarray(t.detach().cpu().numpy() if isinstance(t, torch.Tensor) else t)
+        arr = arr.reshape(-1, width)
+        if arr.shape[0] == 1 and batch != 1:
+            arr = np.repeat(arr, batch, axis=0)
+        return arr.astype(dtype) if arr.shape[0] == batch else None
+
+    return dict(palette_mask=fit(constraints.palette_mask, 10, np.uint8),
+                target_shape=fit(constraints.target_shape, 2, np.int32),
+                palette_penalty=float(constraints.palette_penalty), shape_penalty=float(constraints.shape_penalty),
+                disallow_tokens=tuple(int(t) for t in constraints.disallow_tokens))
 
 
 @dataclass
@@ -67,7 +89,8 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
                     example_ids: np.ndarray | None, max_new: int, stop_on_end: bool = True,
                     forced: np.ndarray | None = None, want_logits: bool = False,
                     max_prefill_tokens: int = DEFAULT_PREFILL_TOKENS, attn_splits: int = 0,
-                    session: Session | None = None, pinned: bool = False) -> GenerationTrace:
+                    session: Session | None = None, pinned: bool = False,
+                    constraints: dict | None = None) -> GenerationTrace:
     """Prefill + greedy decode of a padded batch given as host arrays; returns device tokens.
 
     ``ids`` int [B, S], ``pos`` int [B, S, 3], ``mask`` bool [B, S] (True = real token).  At most
@@ -84,7 +107,7 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
         session = engine.new_session(
             B, t_max, max_new, cap, stop_on_end=stop_on_end, attn_splits=attn_splits,
             forced=None if forced is None else torch.from_numpy(np.ascontiguousarray(forced, dtype=np.int32)),
-            want_step_logits=want_logits)
+            want_step_logits=want_logits, constraints=constraints)
     ex_dev = None
     h2d = 0
     if example_ids is not None and engine.use_example_embedding:
@@ -139,8 +162,6 @@ def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
     """
     if temperature > 0:
         raise NotImplementedError("sampling (temperature > 0) is not implemented on the B200 path")
-    if constraints is not None:
-        raise NotImplementedError("soft decoding constraints are not implemented on the B200 path")
     batch, prompt_len = input_ids.shape
     if attention_mask is not None and tuple(attention_mask.shape) != (batch, prompt_len):
         raise ValueError("attention_mask must have shape [batch, seq_len]")
@@ -158,7 +179,8 @@ def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
     mask = (np.ones((batch, prompt_len), dtype=bool) if attention_mask is None
             else attention_mask.detach().to(torch.bool).cpu().numpy())
     ex = (np.zeros(batch, dtype=np.int64) if example_ids is None else example_ids.detach().cpu().numpy())
-    trace = generate_tokens(engine, ids, pos, mask, ex, max_new, stop_on_end=stop_on_end)
+    trace = generate_tokens(engine, ids, pos, mask, ex, max_new, stop_on_end=stop_on_end,
+                            constraints=_constraints_dict(constraints, batch))
     gen = trace.tokens.to(device=input_ids.device, dtype=input_ids.dtype)
     return torch.cat([input_ids, gen], dim=1)
 
@@ -206,6 +228,59 @@ def build_augmented_prompts(task: dict, test_idx: int, use_train_examples: bool 
     return prompts, positions, info
 
 
+def augmented_constraints(task: dict, test_idx: int, info):
+    """Per-variant colour palettes and output shapes for constrained decoding
+    (src/inference.py:236-282, 798-808): the palette is the set of colours in the train pairs mapped
+    through the variant's colour permutation; the shape is the train outputs' common shape (if any),
+    transposed for the dihedral transforms that swap height and width."""
+    colours: set[int] = set()
+    for pair in task.get("train", []):
+        for key in ("input", "output"):
+            grid = pair.get(key)
+            if grid is not None:
+                colours.update(int(v) for row in grid for v in row)
+    shapes_seen = []
+    for pair in task.get("train", []):
+        g = pair.get("output")
+        if not g or not g[0] or any(len(row) != len(g[0]) for row in g):
+            shapes_seen = None
+            break
+        shapes_seen.append((len(g), len(g[0])))
+    base_shape = shapes_seen[0] if shapes_seen and all(s == shapes_seen[0] for s in shapes_seen) else None
+    palettes, shapes = [], []
+    for d_idx, perm in info:
+        palettes.append(colours if perm is None else {int(perm[c]) for c in colours})
+        if base_shape is None:
+            shapes.append(None)
+        else:
+            shapes.append((base_shape[1], base_shape[0]) if d_idx in (1, 3, 6, 7) else base_shape)
+    return palettes, shapes
+
+
+def chunk_constraints(palettes, shapes, palette_penalty: float, shape_penalty: float) -> DecodingConstraints:
+    """DecodingConstraints of one chunk, built like the reference does (src/inference.py:842-875)."""
+    n = len(palettes)
+    palette_mask = None
+    if any(palettes):
+        m = torch.ones((n, 10), dtype=torch.bool)
+        for i, pal in enumerate(palettes):
+            if pal:
+                m[i] = False
+                for c in pal:
+                    if 0 <= c < 10:
+                        m[i, c] = True
+        palette_mask = m
+    target_shape = None
+    if any(s is not None for s in shapes):
+        t = torch.full((n, 2), -1, dtype=torch.long)
+        for i, s in enumerate(shapes):
+            if s is not None:
+                t[i, 0], t[i, 1] = s[0], s[1]
+        target_shape = t
+    return DecodingConstraints(palette_mask=palette_mask, target_shape=target_shape,
+                               palette_penalty=palette_penalty, shape_penalty=shape_penalty)
+
+
 def pad_prompts(prompts, positions, left: bool = True):
     """Pad ragged prompts to one length with END / (0,0,0) (src/inference.py:878-890)."""
     n = len(prompts)
@@ -236,21 +311,27 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
     reference's batched path does, so each chunk reproduces its semantics (including which
     hidden state yields the first token of a left-padded row).
     """
-    if sample_temperature > 0 or constrain_decoding:
-        raise NotImplementedError("sampling / constrained decoding are not implemented on the B200 path")
+    if sample_temperature > 0:
+        raise NotImplementedError("sampling is not implemented on the B200 path")
     device = torch.device(device)
     engine = _resolve_engine(model, device)
     prompts, positions, info = build_augmented_prompts(task, test_idx, use_train_examples,
                                                        num_color_perms, num_samples)
+    palettes = shapes = None
+    if constrain_decoding:
+        palettes, shapes = augmented_constraints(task, test_idx, info)
     out = []
     for c0 in range(0, len(prompts), max_batch_size):
         chunk = slice(c0, min(c0 + max_batch_size, len(prompts)))
         ids, pos, mask = pad_prompts(prompts[chunk], positions[chunk], left=True)
         ids_t = torch.from_numpy(ids).to(device)
+        cons = None
+        if constrain_decoding:
+            cons = chunk_constraints(palettes[chunk], shapes[chunk], palette_penalty, shape_penalty)
         full = generate_output(engine, ids_t, torch.from_numpy(pos).to(device),
                                torch.full((ids.shape[0],), example_id, dtype=torch.long, device=device),
                                attention_mask=torch.from_numpy(mask).to(device),
-                               max_new_tokens=max_output_tokens, stop_on_end=True)
+                               max_new_tokens=max_output_tokens, stop_on_end=True, constraints=cons)
         rows = full.cpu().tolist()
         for i, toks in enumerate(rows):
             d_idx, tag = info[c0 + i]

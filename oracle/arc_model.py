@@ -173,15 +173,46 @@ def forward(sd: dict, cfg: Config, ids, pos, example_ids=None, mask=None, is_cau
     return F.linear(rmsnorm(x, sd["ln_f.weight"], cfg.norm_eps), sd["lm_head.weight"])
 
 
+def apply_constraints(logits, states, cons):
+    """_apply_logit_constraints (src/inference.py:285-364) on logits [B, 14]; ``states`` are the
+    per-row GridState objects (state after the last fed token).  ``cons`` is a dict with
+    palette_mask [B,10] bool | None, target_shape [B,2] | None, palette_penalty, shape_penalty,
+    disallow_tokens."""
+    if cons is None:
+        return logits
+    logits = logits.clone()
+    for tok in cons.get("disallow_tokens", (10, 12)):
+        logits[:, tok] = float("-inf")
+    pm = cons.get("palette_mask")
+    if pm is not None:
+        logits[:, :10] -= (~pm.bool()).to(logits.dtype) * cons.get("palette_penalty", 2.0)
+    ts = cons.get("target_shape")
+    if ts is not None:
+        pen = cons.get("shape_penalty", 2.0)
+        for b, st in enumerate(states):
+            th, tw = int(ts[b, 0]), int(ts[b, 1])
+            if th < 0 or tw < 0:
+                continue
+            if st.x >= tw:
+                logits[b, :10] -= pen
+            else:
+                logits[b, 11] -= pen
+            if st.y >= th:
+                logits[b, :10] -= pen
+                logits[b, 11] -= pen
+    return logits
+
+
 @dataclass
 class GenResult:
     tokens: torch.Tensor                      # [B, S + n_generated] like generate_output
     logits: list = field(default_factory=list)  # per generated position: [B, 14]
+    picked_from: list = field(default_factory=list)  # the logits the argmax saw (after constraints)
 
 
 @torch.no_grad()
 def generate(sd: dict, cfg: Config, ids, pos, example_ids=None, mask=None, max_new_tokens=900,
-             stop_on_end=True, forced=None, keep_logits=False) -> GenResult:
+             stop_on_end=True, forced=None, keep_logits=False, constraints=None) -> GenResult:
     """generate_output, greedy branch (src/inference.py:487-628), with its helpers _prefill
     (383-424), _decode_step (427-459), StaticKVCache (51-96) and the grid-state tracker.
 
@@ -226,7 +257,9 @@ def generate(sd: dict, cfg: Config, ids, pos, example_ids=None, mask=None, max_n
     logits = F.linear(rmsnorm(x[ar, last_idx], sd["ln_f.weight"], cfg.norm_eps), sd["lm_head.weight"])
 
     all_logits = [logits] if keep_logits else []
-    nxt = logits.argmax(-1)
+    used = apply_constraints(logits, states, constraints)
+    used_logits = [used] if keep_logits else []
+    nxt = used.argmax(-1)
     if forced is not None:
         nxt = forced[:, 0].long()
     out = [ids, nxt[:, None]]
@@ -254,13 +287,15 @@ def generate(sd: dict, cfg: Config, ids, pos, example_ids=None, mask=None, max_n
             x = x + _ffn(sd, p, rmsnorm(x, sd[p + "ln2.weight"], cfg.norm_eps))
         seq_len += 1
         logits = F.linear(rmsnorm(x, sd["ln_f.weight"], cfg.norm_eps), sd["lm_head.weight"])[:, 0]
+        used = apply_constraints(logits, states, constraints)
         if keep_logits:
             all_logits.append(logits)
-        nxt = logits.argmax(-1)
+            used_logits.append(used)
+        nxt = used.argmax(-1)
         if forced is not None:
             nxt = forced[:, step].long()
         if stop_on_end:
             finished |= nxt == END
         out.append(nxt[:, None])
         full_mask[:, S + step] = True
-    return GenResult(torch.cat(out, 1), all_logits)
+    return GenResult(torch.cat(out, 1), all_logits, used_logits)

@@ -71,6 +71,18 @@ def golden_model():
             out[key + "_logits"] = logits.numpy()
             out[key + "_gen"] = toks.numpy()
             out[key + "_gen_nostop"] = toks_nostop.numpy()
+        # soft-constrained decoding (palette + target shape + disallowed tokens), right-padded batch
+        ids, pos, mask = pad_prompts(prompts, positions, left=False)
+        pm = torch.tensor([[1, 1, 0, 0, 1, 0, 0, 0, 0, 1], [1, 0, 1, 1, 0, 0, 1, 0, 0, 0], [1] * 10], dtype=torch.bool)
+        ts = torch.tensor([[3, 4], [-1, -1], [2, 2]])
+        cons = rinf.DecodingConstraints(palette_mask=pm, target_shape=ts, palette_penalty=1.5, shape_penalty=2.5)
+        with torch.no_grad():
+            toks_c = rinf.generate_output(model, torch.from_numpy(ids), torch.from_numpy(pos), torch.tensor([3, 0, 7]),
+                                          torch.from_numpy(mask), max_new_tokens=32, stop_on_end=False,
+                                          constraints=cons)
+        out[f"{wname}_constrained_gen"] = toks_c.numpy()
+        out[f"{wname}_constrained_palette"] = pm.numpy()
+        out[f"{wname}_constrained_shape"] = ts.numpy()
         # no mask, no example ids: plain causal forward
         ids, pos, _ = pad_prompts(prompts[:1], positions[:1], left=False)
         with torch.no_grad():
@@ -110,7 +122,24 @@ def golden_tokens():
         gs_cases.append({"tokens": toks, "cut": cut, "init": [int(x), int(y), bool(io)], "track": track})
     long_row = [[1] * 40 for _ in range(35)]  # exceeds the clamps
     long_toks = rdata.encode_example(long_row, None)
+    # constrained-decoding host helpers on a synthetic task with a common output shape
+    ctask = synthetic.capped_tasks(5, 1, 3, 3, 2, 5, None)[0]
+    shape0 = (len(ctask["train"][0]["output"]), len(ctask["train"][0]["output"][0]))
+    for pair in ctask["train"][1:]:
+        pair["output"] = [row[:shape0[1]] + [0] * max(0, shape0[1] - len(row)) for row in pair["output"][:shape0[0]]]
+        while len(pair["output"]) < shape0[0]:
+            pair["output"].append([0] * shape0[1])
+    base_palette = sorted(rinf._collect_palette(ctask, 0))
+    base_shape = rinf._infer_output_shape(ctask)
+    perms = rdata.generate_color_permutations(3, seed=42)
+    con_rows = []
+    for d in range(8):
+        for p in range(3):
+            pal = sorted({int(perms[p][c]) for c in base_palette}) if p > 0 else base_palette
+            shp = rinf._transform_shape(base_shape, d)
+            con_rows.append({"dihedral": d, "perm": p, "palette": pal, "shape": list(shp) if shp else None})
     out = {
+        "constraint_task": ctask, "constraint_rows": con_rows,
         "cases": cases, "streams": streams, "decoded": decoded, "grid_state": gs_cases,
         "perms20": rdata.generate_color_permutations(20, seed=42).tolist(),
         "perms3_seed7": rdata.generate_color_permutations(3, seed=7).tolist(),

@@ -128,3 +128,23 @@ def test_no_cpu_fallback():
     with pytest.raises(ValueError):
         generate_output(M(), torch.zeros(1, 4, dtype=torch.long), torch.zeros(1, 4, 3, dtype=torch.long),
                         attention_mask=torch.ones(2, 4, dtype=torch.bool))
+
+
+def test_constraint_helpers_match_reference(golden_tokens):
+    pytest.importorskip("torch")
+    from mdlarc_scale_b200.inference import augmented_constraints, build_augmented_prompts, chunk_constraints
+    task = golden_tokens["constraint_task"]
+    _, _, info = build_augmented_prompts(task, 0, True, 3, 1)
+    palettes, shapes = augmented_constraints(task, 0, info)
+    rows = golden_tokens["constraint_rows"]
+    assert len(rows) == len(info) == 24
+    for row, (d, perm), pal, shp in zip(rows, info, palettes, shapes):
+        assert d == row["dihedral"] and (perm is None) == (row["perm"] == 0)
+        assert sorted(pal) == row["palette"]
+        assert (list(shp) if shp else None) == row["shape"]
+    cons = chunk_constraints(palettes[:5], shapes[:5], 2.0, 3.0)
+    assert cons.palette_mask.shape == (5, 10) and cons.target_shape.shape == (5, 2)
+    for i in range(5):
+        assert sorted(cons.palette_mask[i].nonzero().flatten().tolist()) == sorted(palettes[i])
+        assert cons.target_shape[i].tolist() == list(shapes[i])
+    assert cons.palette_penalty == 2.0 and cons.shape_penalty == 3.0 and cons.disallow_tokens == (10, 12)

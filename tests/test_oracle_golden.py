@@ -108,3 +108,19 @@ def test_votes(golden_votes):
         assert [[g, n] for g, n in votes] == c["votes"]
         assert ov.aaivr_predict(preds, 2, c["test_input"], rng=random.Random(c["seed"])) == c["top2"]
         assert ov.aaivr_predict(preds, 3, c["test_input"], False, random.Random(c["seed"] + 100)) == c["top3_keep_copies"]
+
+
+def test_constrained_generate_matches_reference(golden_model):
+    for name in ("plain", "varied"):
+        cfg, sd = _weights(name)
+        k = f"{name}_right"
+        cons = dict(palette_mask=torch.from_numpy(golden_model[f"{name}_constrained_palette"]),
+                    target_shape=torch.from_numpy(golden_model[f"{name}_constrained_shape"]),
+                    palette_penalty=1.5, shape_penalty=2.5, disallow_tokens=(10, 12))
+        got = om.generate(sd, cfg, torch.from_numpy(golden_model[k + "_ids"]), torch.from_numpy(golden_model[k + "_pos"]),
+                          torch.from_numpy(golden_model[k + "_ex"]), torch.from_numpy(golden_model[k + "_mask"]),
+                          max_new_tokens=32, stop_on_end=False, constraints=cons).tokens.numpy()
+        assert np.array_equal(got, golden_model[f"{name}_constrained_gen"])
+        # the constraints really bite: the unconstrained continuation differs
+        S = golden_model[k + "_ids"].shape[1]
+        assert not np.array_equal(got[:, S:S + 24], golden_model[k + "_gen_nostop"][:, S:S + 24])
