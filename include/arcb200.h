@@ -134,6 +134,15 @@ typedef struct arcb_session_desc {
   float palette_penalty;
   float shape_penalty;
   uint32_t disallow_token_mask;  /* bit t set: token t gets -inf (reference default: START, IO_SEP) */
+  /* Sampling (src/inference.py:575-583, 612-620): temperature <= 0 = greedy argmax.  Otherwise the
+   * (constrained) logits are divided by max(temperature, 1e-6), optionally cut to the top_k largest
+   * (0 = all), soft-maxed and sampled by inverse CDF with the uniform number
+   * u = splitmix64(sample_seed, row, generated index) >> 40 scaled to [0, 1): a counter-based
+   * stream, reproducible for a seed and independent of batch shape (torch.multinomial's stream
+   * cannot be reproduced on the device). */
+  float temperature;
+  int32_t top_k;
+  uint64_t sample_seed;
 } arcb_session_desc;
 
 int64_t arcb_session_workspace_bytes(const arcb_engine* eng, int32_t n_seqs,

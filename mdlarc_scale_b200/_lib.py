@@ -52,6 +52,7 @@ class SessionDesc(C.Structure):
         ("d_out_tokens", C.c_void_p), ("d_forced", C.c_void_p), ("d_step_logits", C.c_void_p),
         ("d_palette_mask", C.c_void_p), ("d_target_shape", C.c_void_p),
         ("palette_penalty", C.c_float), ("shape_penalty", C.c_float), ("disallow_token_mask", C.c_uint32),
+        ("temperature", C.c_float), ("top_k", C.c_int32), ("sample_seed", C.c_uint64),
     ]
 
 

@@ -334,6 +334,9 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
   st.palette_penalty = dsc->palette_penalty;
   st.shape_penalty = dsc->shape_penalty;
   st.disallow_mask = dsc->disallow_token_mask & 0x3fffu;
+  st.temperature = dsc->temperature;
+  st.top_k = dsc->top_k;
+  st.sample_seed = dsc->sample_seed;
   st.err = e->d_err;
   cudaError_t r = cudaMemset(ints, 0, w.n_int * 4);
   if (r != cudaSuccess) { delete s; return fail_cuda(r, "cudaMemset(session state)"); }

@@ -184,7 +184,7 @@ head_kernel(HeadArgs a, DecodeState st) {
   }
   // Soft constraints (src/inference.py:285-364) act on a copy of the logits, using the grid state
   // after the last fed token (st.gx / st.gy were advanced by decode_begin, or armed just above).
-  if (st.disallow_mask || st.palette_mask || st.target_shape) {
+  if (st.disallow_mask || st.palette_mask || st.target_shape || st.temperature > 0.f) {
     float adj[ARCB_VOCAB];
 #pragma unroll
     for (int v = 0; v < ARCB_VOCAB; ++v) adj[v] = ((st.disallow_mask >> v) & 1u) ? -INFINITY : acc[v];
@@ -216,6 +216,37 @@ head_kernel(HeadArgs a, DecodeState st) {
 #pragma unroll
     for (int v = 1; v < ARCB_VOCAB; ++v)
       if (adj[v] > bv2) { bv2 = adj[v]; best = v; }
+    if (st.temperature > 0.f) {
+      // temperature / top-k sampling (src/inference.py:575-583): softmax of the kept logits, inverse CDF
+      const float inv_t = 1.f / fmaxf(st.temperature, 1e-6f);
+      const int kk = (st.top_k > 0 && st.top_k < ARCB_VOCAB) ? st.top_k : ARCB_VOCAB;
+      float p[ARCB_VOCAB];
+      float total = 0.f;
+#pragma unroll
+      for (int v = 0; v < ARCB_VOCAB; ++v) {
+        int rank = 0;  // logits ahead of v: larger, or equal with a smaller index
+#pragma unroll
+        for (int w = 0; w < ARCB_VOCAB; ++w) rank += (adj[w] > adj[v] || (adj[w] == adj[v] && w < v)) ? 1 : 0;
+        p[v] = (rank < kk) ? __expf((adj[v] - bv2) * inv_t) : 0.f;
+        total += p[v];
+      }
+      // counter-based uniform number: splitmix64 of (seed, row, generated index)
+      unsigned long long z = st.sample_seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(b + 1) +
+                             0xD1B54A32D192ED03ull * (unsigned long long)(out_idx + 1);
+      z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+      z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+      z ^= z >> 31;
+      const float u = (float)(z >> 40) * (1.f / 16777216.f) * total;
+      float run = 0.f;
+      int pick = best;
+      bool found = false;
+#pragma unroll
+      for (int v = 0; v < ARCB_VOCAB; ++v) {
+        run += p[v];
+        if (!found && p[v] > 0.f && u < run) { pick = v; found = true; }
+      }
+      best = pick;
+    }
   }
   int tok = best;
   const bool in_range = out_idx >= 0 && out_idx < st.max_new;

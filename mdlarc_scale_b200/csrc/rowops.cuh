@@ -22,6 +22,10 @@ struct DecodeState {
   const int* target_shape;            // [B][2] (h, w), negative = none
   float palette_penalty, shape_penalty;
   unsigned int disallow_mask;         // bit t: token t -> -inf
+  // sampling: temperature <= 0 = greedy
+  float temperature;
+  int top_k;
+  unsigned long long sample_seed;
   int* err;
 };
 

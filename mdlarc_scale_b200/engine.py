@@ -146,9 +146,10 @@ class Engine:
     def new_session(self, n_seqs: int, t_max: int, max_new: int, max_prefill_tokens: int,
                     stop_on_end: bool = True, attn_splits: int = 0, forced: torch.Tensor | None = None,
                     want_step_logits: bool = False, out_tokens: torch.Tensor | None = None,
-                    constraints: dict | None = None) -> "Session":
+                    constraints: dict | None = None, temperature: float = 0.0, top_k: int = 0,
+                    sample_seed: int = 0) -> "Session":
         return Session(self, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end, attn_splits,
-                       forced, want_step_logits, out_tokens, constraints)
+                       forced, want_step_logits, out_tokens, constraints, temperature, top_k, sample_seed)
 
 
 _ENGINES: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
@@ -174,7 +175,8 @@ class Session:
     """A static KV cache, the greedy-loop state and the decode graph for ``n_seqs`` sequences."""
 
     def __init__(self, eng: Engine, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end,
-                 attn_splits, forced, want_step_logits, out_tokens=None, constraints=None):
+                 attn_splits, forced, want_step_logits, out_tokens=None, constraints=None,
+                 temperature=0.0, top_k=0, sample_seed=0):
         self.eng = eng
         self.n_seqs, self.t_max, self.max_new = int(n_seqs), int(t_max), int(max_new)
         self.max_prefill_tokens = int(max_prefill_tokens)
@@ -226,7 +228,8 @@ class Session:
             d_out_tokens=self.out_tokens.data_ptr(), d_forced=_ptr(self.forced),
             d_step_logits=_ptr(self.step_logits),
             d_palette_mask=_ptr(self.palette_mask), d_target_shape=_ptr(self.target_shape),
-            palette_penalty=pal_pen, shape_penalty=shp_pen, disallow_token_mask=disallow)
+            palette_penalty=pal_pen, shape_penalty=shp_pen, disallow_token_mask=disallow,
+            temperature=float(temperature), top_k=int(top_k or 0), sample_seed=int(sample_seed) & (2 ** 64 - 1))
         self._handle = C.c_void_p()
         with torch.cuda.device(dev):
             _lib.check(lib.arcb_session_create(eng._handle, C.byref(desc), C.byref(self._handle)))

@@ -1,8 +1,9 @@
 """Drop-in for the reference's generation API (``src/inference.py``) on the B200 engine.
 
 ``generate_output`` and ``predict_with_augmentations`` keep the reference's signatures, argument
-meaning and error behaviour; greedy decoding, with or without the soft palette / shape constraints,
-is implemented natively (sampling raises ``NotImplementedError`` rather than falling back).
+meaning and error behaviour: greedy decoding, temperature / top-k sampling and the soft palette /
+shape constraints all run on the device (sampling uses a counter-based random stream seeded from
+torch's default generator; it cannot reproduce ``torch.multinomial`` draw for draw).
 
 Differences from the reference that are part of the design:
   * prompts are packed (no padded positions are computed) and the KV cache is compacted, which
@@ -90,7 +91,8 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
                     forced: np.ndarray | None = None, want_logits: bool = False,
                     max_prefill_tokens: int = DEFAULT_PREFILL_TOKENS, attn_splits: int = 0,
                     session: Session | None = None, pinned: bool = False,
-                    constraints: dict | None = None) -> GenerationTrace:
+                    constraints: dict | None = None, temperature: float = 0.0, top_k: int | None = None,
+                    sample_seed: int = 0) -> GenerationTrace:
     """Prefill + greedy decode of a padded batch given as host arrays; returns device tokens.
 
     ``ids`` int [B, S], ``pos`` int [B, S, 3], ``mask`` bool [B, S] (True = real token).  At most
@@ -107,7 +109,8 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
         session = engine.new_session(
             B, t_max, max_new, cap, stop_on_end=stop_on_end, attn_splits=attn_splits,
             forced=None if forced is None else torch.from_numpy(np.ascontiguousarray(forced, dtype=np.int32)),
-            want_step_logits=want_logits, constraints=constraints)
+            want_step_logits=want_logits, constraints=constraints, temperature=temperature,
+            top_k=top_k or 0, sample_seed=sample_seed)
     ex_dev = None
     h2d = 0
     if example_ids is not None and engine.use_example_embedding:
@@ -159,9 +162,8 @@ def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
     ``model`` is a reference ``TinyTransformer`` (its weights are packed once and cached) or an
     ``Engine``.  Returns ``[batch, seq_len + n_generated]`` int64 on ``input_ids.device``.
     ``use_compile`` is accepted and ignored: the decode step always runs as a CUDA graph.
+    ``temperature > 0`` samples (optionally from the ``top_k`` largest logits) instead of argmax.
     """
-    if temperature > 0:
-        raise NotImplementedError("sampling (temperature > 0) is not implemented on the B200 path")
     batch, prompt_len = input_ids.shape
     if attention_mask is not None and tuple(attention_mask.shape) != (batch, prompt_len):
         raise ValueError("attention_mask must have shape [batch, seq_len]")
@@ -179,8 +181,14 @@ def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
     mask = (np.ones((batch, prompt_len), dtype=bool) if attention_mask is None
             else attention_mask.detach().to(torch.bool).cpu().numpy())
     ex = (np.zeros(batch, dtype=np.int64) if example_ids is None else example_ids.detach().cpu().numpy())
+    seed = 0
+    if temperature > 0:
+        # one draw from torch's default generator per call, so torch.manual_seed makes sampling
+        # reproducible as it does for the reference (whose torch.multinomial stream cannot be matched)
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item())
     trace = generate_tokens(engine, ids, pos, mask, ex, max_new, stop_on_end=stop_on_end,
-                            constraints=_constraints_dict(constraints, batch))
+                            constraints=_constraints_dict(constraints, batch), temperature=float(temperature),
+                            top_k=top_k, sample_seed=seed)
     gen = trace.tokens.to(device=input_ids.device, dtype=input_ids.dtype)
     return torch.cat([input_ids, gen], dim=1)
 
@@ -311,8 +319,6 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
     reference's batched path does, so each chunk reproduces its semantics (including which
     hidden state yields the first token of a left-padded row).
     """
-    if sample_temperature > 0:
-        raise NotImplementedError("sampling is not implemented on the B200 path")
     device = torch.device(device)
     engine = _resolve_engine(model, device)
     prompts, positions, info = build_augmented_prompts(task, test_idx, use_train_examples,
@@ -331,7 +337,8 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
         full = generate_output(engine, ids_t, torch.from_numpy(pos).to(device),
                                torch.full((ids.shape[0],), example_id, dtype=torch.long, device=device),
                                attention_mask=torch.from_numpy(mask).to(device),
-                               max_new_tokens=max_output_tokens, stop_on_end=True, constraints=cons)
+                               max_new_tokens=max_output_tokens, temperature=sample_temperature,
+                               top_k=sample_top_k, stop_on_end=True, constraints=cons)
         rows = full.cpu().tolist()
         for i, toks in enumerate(rows):
             d_idx, tag = info[c0 + i]

@@ -264,3 +264,37 @@ def test_constrained_generation_vs_reference(engines, golden_model, name):
         # the margin that matters is the one of the penalised logits the argmax saw
         ok, where = tokens_agree(g, w, [lg[b].numpy() for lg in ref.picked_from], TOL)
         assert ok, f"row {b} diverges at generated index {where} with a clear reference margin"
+
+
+def test_sampling_distribution_and_reproducibility(engines):
+    """Temperature / top-k sampling on the device: 4096 identical rows sample their first token; the
+    empirical distribution must match softmax(logits / T) (restricted to the top-k), a seed must
+    reproduce the draw and a tiny temperature must reduce to the argmax."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    eng, cfg, sd = engines["varied", "tc-flash"]
+    task = synthetic.capped_tasks(81, 1, 1, 1, 2, 4, None)
+    prompts, positions = synthetic.prompts_for(task)
+    n = 4096
+    ids, pos, mask = pad_prompts(prompts * n, positions * n, left=False)
+    T = 0.7
+    a = generate_tokens(eng, ids, pos, mask, None, 2, stop_on_end=False, want_logits=True, temperature=T, sample_seed=11)
+    logits = a.first_logits[0].double().cpu()
+    assert (a.first_logits - a.first_logits[0]).abs().max().item() < 1e-4   # identical rows, identical logits
+    first = a.tokens[:, 0].cpu()
+    want = torch.softmax(logits / T, -1)
+    freq = torch.bincount(first.long(), minlength=14).double() / n
+    assert (freq - want).abs().max().item() < 0.03, (freq, want)
+    b = generate_tokens(eng, ids, pos, mask, None, 2, stop_on_end=False, temperature=T, sample_seed=11)
+    assert torch.equal(a.tokens.cpu(), b.tokens.cpu())
+    c = generate_tokens(eng, ids, pos, mask, None, 2, stop_on_end=False, temperature=T, sample_seed=12)
+    assert not torch.equal(a.tokens.cpu(), c.tokens.cpu())
+    k3 = generate_tokens(eng, ids, pos, mask, None, 2, stop_on_end=False, temperature=T, top_k=3, sample_seed=5)
+    top3 = torch.topk(logits, 3).indices
+    f3 = torch.bincount(k3.tokens[:, 0].long().cpu(), minlength=14).double() / n
+    w3 = torch.zeros(14, dtype=torch.double)
+    w3[top3] = torch.softmax(logits[top3] / T, -1)
+    assert f3[[i for i in range(14) if i not in top3.tolist()]].sum().item() == 0.0
+    assert (f3 - w3).abs().max().item() < 0.03
+    cold = generate_tokens(eng, ids[:8], pos[:8], mask[:8], None, 2, stop_on_end=False, temperature=1e-4, sample_seed=3)
+    assert (cold.tokens[:, 0].cpu() == int(logits.argmax())).all()
