@@ -193,3 +193,63 @@ def inverse_color_perm(perm) -> np.ndarray:
 def apply_color_perm_grid(grid: Grid, perm) -> Grid:
     lut = [int(v) for v in perm]
     return [[lut[c] for c in row] for row in grid]
+
+
+# ---------------------------------------------------------------------------
+# vectorised serialisation (same tokens and positions as the loops above, for rectangular grids)
+# ---------------------------------------------------------------------------
+def dihedral_np(grid: np.ndarray, idx: int) -> np.ndarray:
+    """DIHEDRAL_TRANSFORMS[idx] on a 2-D array."""
+    if idx == 0:
+        return grid
+    if idx == 1:
+        return np.rot90(grid, -1)
+    if idx == 2:
+        return np.rot90(grid, 2)
+    if idx == 3:
+        return np.rot90(grid, 1)
+    if idx == 4:
+        return grid[:, ::-1]
+    if idx == 5:
+        return grid[::-1]
+    if idx == 6:
+        return grid.T
+    if idx == 7:
+        return np.rot90(grid, 2).T
+    raise ValueError(idx)
+
+
+def _grid_tokens_positions(grid: np.ndarray, z: int):
+    """Row-major cells with a NEWLINE after every row, and their (x, y, z) positions."""
+    h, w = grid.shape
+    toks = np.empty((h, w + 1), dtype=np.int64)
+    toks[:, :w] = grid
+    toks[:, w] = NEWLINE_TOKEN_ID
+    pos = np.empty((h, w + 1, 3), dtype=np.int64)
+    pos[:, :w, 0] = np.minimum(np.arange(w), MAX_X)[None, :]
+    pos[:, w, 0] = 0
+    pos[:, :, 1] = np.minimum(np.arange(h), MAX_Y)[:, None]
+    pos[:, :, 2] = z
+    return toks.reshape(-1), pos.reshape(-1, 3)
+
+
+def encode_example_np(input_grid: np.ndarray, output_grid: np.ndarray | None = None):
+    """encode_example + compute_positions_3d of one pair as arrays (tokens [n], positions [n, 3])."""
+    ti, pi = _grid_tokens_positions(input_grid, 1)
+    parts_t = [np.array([START_TOKEN_ID]), ti, np.array([IO_SEP_TOKEN_ID])]
+    parts_p = [np.zeros((1, 3), np.int64), pi, np.array([[0, 0, 2]])]
+    if output_grid is not None:
+        to, po = _grid_tokens_positions(output_grid, 3)
+        parts_t += [to, np.array([END_TOKEN_ID])]
+        parts_p += [po, np.array([[0, 0, 4]])]
+    return np.concatenate(parts_t), np.concatenate(parts_p)
+
+
+def as_rect_array(grid) -> np.ndarray | None:
+    """2-D int array of a non-empty rectangular grid, else None."""
+    if not grid or not grid[0]:
+        return None
+    w = len(grid[0])
+    if any(len(r) != w for r in grid):
+        return None
+    return np.asarray(grid, dtype=np.int64)

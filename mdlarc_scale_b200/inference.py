@@ -19,8 +19,9 @@ from dataclasses import dataclass
 import numpy as np
 import torch
 
-from .data import (DIHEDRAL_TRANSFORMS, END_TOKEN_ID, IO_SEP_TOKEN_ID, apply_color_perm_grid,
-                   compute_positions_3d, decode_output_grid, encode_example, generate_color_permutations)
+from .data import (DIHEDRAL_TRANSFORMS, END_TOKEN_ID, IO_SEP_TOKEN_ID, apply_color_perm_grid, as_rect_array,
+                   compute_positions_3d, decode_output_grid, dihedral_np, encode_example, encode_example_np,
+                   generate_color_permutations)
 from .engine import Engine, Session, chunk_rows, engine_for, plan_prefill
 
 DEFAULT_PREFILL_TOKENS = 65536  # packed prompt tokens per prefill call (bounds the workspace)
@@ -209,6 +210,27 @@ def build_augmented_prompts(task: dict, test_idx: int, use_train_examples: bool 
     test_input = task["test"][test_idx]["input"]
     perms = generate_color_permutations(num_color_perms, seed=42)
     prompts, positions, info = [], [], []
+    # vectorised path for well-formed (rectangular, colours 0-9) grids: same tokens and positions
+    arrs = [(as_rect_array(p["input"]), as_rect_array(p["output"])) for p in train_pairs]
+    t_arr = as_rect_array(test_input)
+    if t_arr is not None and all(a is not None and b is not None for a, b in arrs) and \
+            all(int(g.min()) >= 0 and int(g.max()) <= 9 for pair in arrs + [(t_arr, t_arr)] for g in pair):
+        for d_idx in range(8):
+            d_in = [dihedral_np(a, d_idx) for a, _ in arrs]
+            d_out = [dihedral_np(b, d_idx) for _, b in arrs]
+            d_tst = dihedral_np(t_arr, d_idx)
+            for p_idx in range(num_color_perms):
+                lut = perms[p_idx]
+                tag = tuple(int(v) for v in lut) if p_idx > 0 else None
+                parts = [encode_example_np(lut[gi], lut[go]) for gi, go in zip(d_in, d_out)]
+                parts.append(encode_example_np(lut[d_tst], None))
+                toks = np.concatenate([t for t, _ in parts])
+                pos = np.concatenate([q for _, q in parts])
+                for _ in range(max(1, num_samples)):
+                    prompts.append(toks)
+                    positions.append(pos)
+                    info.append((d_idx, tag))
+        return prompts, positions, info
     for d_idx, fn in enumerate(DIHEDRAL_TRANSFORMS):
         ins = [fn(p["input"]) for p in train_pairs]
         outs = [fn(p["output"]) for p in train_pairs]
