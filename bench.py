@@ -145,7 +145,9 @@ def run_reference(args, rank):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1000 * float(np.mean(times)), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "cfg4-large-decode (bounded CPU sample)", "model": MODEL_SIZE},
+        "config": {"workload": "cfg4-large-decode", "model": MODEL_SIZE, "sequences_per_gpu_per_step": args.batch,
+                   "new_tokens": MAX_NEW, "kv_positions": KV_POSITIONS, "stop_on_end": False,
+                   "note": "CPU arm: each step is a bounded sample of this workload (see cpu_baseline.sample)"},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
