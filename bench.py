@@ -311,6 +311,13 @@ def run_ours(args, rank, world, local_rank):
         barrier()
     launches = int(lib.arcb_launch_count(0))
     session.poll()
+    # live sample from inside the timed region: the layer-0 attention launch of the LAST decode step
+    # (event nodes in the step graph); every row is then at prompt length + MAX_NEW - 1 cached positions
+    try:
+        live_ms = session.attention_probe_ms()
+    except RuntimeError:
+        live_ms = float("nan")
+    live_bytes = float((resident[n_total - 1][1] + (MAX_NEW - 1)).sum()) * engine.n_heads * 64 * 2 * 2
     dt = e0.elapsed_time(e1) / 1e3
     prefill_tokens = int(sum(int(r[1].sum()) for r in resident[args.warmup:]))
     # prefill share, device-timed on the same inputs (one extra untimed-for-value pass)
@@ -388,7 +395,11 @@ def run_ours(args, rank, world, local_rank):
             "roofline": {"bound": "hbm", "achieved": attn_gbs, "peak": peak, "unit": "GB/s",
                          "frac": attn_gbs / peak, "traffic": attn_bytes * ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE, "peak_kind": peak_kind,
                          "kernel": "attn_stream_kernel (decode attention)", "ms_per_launch": attn_ms,
-                         "algorithmic_bytes_per_launch": attn_bytes},
+                         "algorithmic_bytes_per_launch": attn_bytes,
+                         "in_graph_sample": {"what": "layer-0 attention launch of the last timed decode step, "
+                                                     "CUDA event nodes inside the step graph",
+                                             "ms": live_ms, "algorithmic_bytes": live_bytes,
+                                             "gbs": live_bytes / live_ms / 1e6}},
             "prefill": {"tokens_per_s_per_gpu": prefill_tok_s, "tokens_per_step": prefill_tokens // args.steps},
         }
         if not args.no_cpu and world == 1:

@@ -202,6 +202,11 @@ int arcb_decode(arcb_session* s, int32_t n_steps, void* stream);
  * device error word (0 = none). Replaces `finished.all()` (src/inference.py:594). */
 int arcb_session_poll(arcb_session* s, int32_t* n_finished, int32_t* device_error, void* stream);
 
+/* Device time (ms) of the layer-0 decode-attention launch (split kernel + combine) in the most
+ * recent decode step: an event pair recorded as nodes of the step graph.  A measurement aid with no
+ * counterpart in the reference; the cached lengths it ran at are prompt length + generated so far. */
+int arcb_session_attention_probe(arcb_session* s, float* ms);
+
 /* Number of kernels the library has launched since the counter was last reset
  * (graph replays count the kernels inside the graph). */
 int64_t arcb_launch_count(int reset);
@@ -256,6 +261,87 @@ int arcb_op_decode_attention_static(const void* d_q16, const void* d_k, const vo
 int arcb_op_head(const float* d_x, const int32_t* d_row_index, const float* d_lnf_w,
                  const float* d_lm_head, float* d_logits, int32_t* d_argmax, int32_t rows,
                  int32_t d, float eps, void* stream);
+
+/* --------------------------------------------------------------------------
+ * Augmentation fan-out on the device (integer / byte work, bit-exact).
+ *
+ * Replaces the per-cell Python loops either side of generation: prompt construction for every
+ * (dihedral x colour permutation) variant of a task (src/inference.py:794-827 with
+ * src/data.py:40-93, 124-233 and src/inference.py:1006-1008) and the way back from generated
+ * tokens to a canonical candidate grid (src/inference.py:906-915, src/data.py:95-117,
+ * src/voting.py:19-54, 57-108).
+ * -------------------------------------------------------------------------- */
+
+/* Grids of the tasks, uploaded once: row-major uint8 cells, one (offset, h, w) triple per grid.
+ * A prompt template lists the grids of one (task, test input) in prompt order: train input 0,
+ * train output 0, ..., test input (odd entries are outputs), at most ARCB_MAX_TEMPLATE_GRIDS. */
+#define ARCB_MAX_TEMPLATE_GRIDS 64
+typedef struct arcb_prompt_build_args {
+  int32_t n_variants;
+  int32_t n_perms;                 /* rows of d_perm_lut */
+  const uint8_t* d_cells;
+  const int32_t* d_grid_off;       /* [n_grids] first cell of each grid */
+  const int32_t* d_grid_h;         /* [n_grids] */
+  const int32_t* d_grid_w;         /* [n_grids] */
+  const int32_t* d_tpl_off;        /* [n_templates + 1] range of each template in d_tpl_grid */
+  const int32_t* d_tpl_grid;       /* grid ids */
+  const uint8_t* d_perm_lut;       /* [n_perms][10] old colour -> new colour */
+  /* per variant */
+  const int32_t* d_var_template;
+  const int32_t* d_var_dihedral;   /* 0..7, the order of src/data.py:224-233 */
+  const int32_t* d_var_perm;       /* row of d_perm_lut */
+  const int32_t* d_var_tok_off;    /* [n_variants + 1] first packed token of each variant */
+  const int32_t* d_var_seq;        /* cache row of each variant */
+  /* packed outputs, [d_var_tok_off[n_variants]] each (d_pos_xyz three per token): the arrays
+   * arcb_prefill_args takes for unpadded causal prompts (kv_slot = index in the sequence,
+   * kv_count = kv_slot + 1, kv_row = packed index). Any may be NULL. */
+  int32_t* d_token_ids;
+  int32_t* d_pos_xyz;
+  int32_t* d_seq;
+  int32_t* d_kv_slot;
+  int32_t* d_kv_count;
+  int32_t* d_kv_row;
+  int32_t* d_status;               /* optional: set to a non-zero ARCB_DEV_* code when a variant's
+                                      length differs from its d_var_tok_off range or a template is
+                                      too long; the variant is then left unwritten */
+} arcb_prompt_build_args;
+
+int arcb_build_prompts(const arcb_prompt_build_args* args, void* stream);
+
+/* One fixed-width record per generated sequence: the candidate grid mapped back to the task's own
+ * orientation and colours. status: 0 = no grid (nothing between the last IO_SEP and END),
+ * 1 = rectangular grid, 2 = malformed (jagged or only separators). input_copy = 1 when the grid as
+ * generated (before mapping back) equals the task's test input, which is the comparison
+ * src/voting.py:92 makes. */
+#define ARCB_CANDIDATE_MAX_CELLS 936
+typedef struct arcb_candidate_record {
+  uint8_t status;
+  uint8_t input_copy;
+  uint16_t h;
+  uint16_t w;
+  uint16_t n_tokens;               /* generated tokens up to and including the first END */
+  uint8_t cells[ARCB_CANDIDATE_MAX_CELLS];   /* row-major h x w */
+} arcb_candidate_record;           /* 944 bytes */
+
+typedef struct arcb_candidate_args {
+  int32_t n_rows;
+  int32_t max_new;                 /* tokens per row, <= ARCB_CANDIDATE_MAX_CELLS */
+  const int32_t* d_tokens;         /* [n_rows][max_new] generated tokens (the session's d_out_tokens) */
+  const int32_t* d_row_dihedral;   /* [n_rows] transform the prompt was built with; < 0 = padding row */
+  const int32_t* d_row_perm;       /* [n_rows] row of d_perm_lut */
+  const uint8_t* d_perm_lut;       /* [n_perms][10] old -> new (the forward map; inverted here) */
+  int32_t n_perms;
+  int32_t reserved;
+  /* optional test inputs for the input-copy flag */
+  const int32_t* d_row_test_grid;  /* [n_rows] grid id, < 0 = none */
+  const uint8_t* d_cells;
+  const int32_t* d_grid_off;
+  const int32_t* d_grid_h;
+  const int32_t* d_grid_w;
+  arcb_candidate_record* d_records; /* [n_rows] */
+} arcb_candidate_args;
+
+int arcb_canonicalize_candidates(const arcb_candidate_args* args, void* stream);
 
 #ifdef __cplusplus
 }

@@ -26,9 +26,9 @@ EXPORTS = [
     "arcb_last_error", "arcb_device_ok", "arcb_engine_create", "arcb_engine_destroy",
     "arcb_engine_load_tensor", "arcb_session_workspace_bytes", "arcb_kv_cache_bytes",
     "arcb_session_create", "arcb_session_destroy", "arcb_prefill", "arcb_decode",
-    "arcb_session_poll", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
+    "arcb_session_poll", "arcb_session_attention_probe", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
     "arcb_attn_scratch_bytes", "arcb_op_decode_attention", "arcb_op_decode_attention_static",
-    "arcb_op_head",
+    "arcb_op_head", "arcb_build_prompts", "arcb_canonicalize_candidates",
 ]
 STATIC_ATTN_MAX_RECORDS = 16384
 
@@ -70,6 +70,29 @@ class PrefillArgs(C.Structure):
     ]
 
 
+class PromptBuildArgs(C.Structure):
+    _fields_ = [
+        ("n_variants", C.c_int32), ("n_perms", C.c_int32),
+        ("d_cells", C.c_void_p), ("d_grid_off", C.c_void_p), ("d_grid_h", C.c_void_p), ("d_grid_w", C.c_void_p),
+        ("d_tpl_off", C.c_void_p), ("d_tpl_grid", C.c_void_p), ("d_perm_lut", C.c_void_p),
+        ("d_var_template", C.c_void_p), ("d_var_dihedral", C.c_void_p), ("d_var_perm", C.c_void_p),
+        ("d_var_tok_off", C.c_void_p), ("d_var_seq", C.c_void_p),
+        ("d_token_ids", C.c_void_p), ("d_pos_xyz", C.c_void_p), ("d_seq", C.c_void_p),
+        ("d_kv_slot", C.c_void_p), ("d_kv_count", C.c_void_p), ("d_kv_row", C.c_void_p),
+        ("d_status", C.c_void_p),
+    ]
+
+
+class CandidateArgs(C.Structure):
+    _fields_ = [
+        ("n_rows", C.c_int32), ("max_new", C.c_int32),
+        ("d_tokens", C.c_void_p), ("d_row_dihedral", C.c_void_p), ("d_row_perm", C.c_void_p),
+        ("d_perm_lut", C.c_void_p), ("n_perms", C.c_int32), ("reserved", C.c_int32),
+        ("d_row_test_grid", C.c_void_p), ("d_cells", C.c_void_p), ("d_grid_off", C.c_void_p),
+        ("d_grid_h", C.c_void_p), ("d_grid_w", C.c_void_p), ("d_records", C.c_void_p),
+    ]
+
+
 _lib = None
 
 
@@ -105,6 +128,9 @@ def load() -> C.CDLL:
     lib.arcb_prefill.argtypes = [vp, C.POINTER(PrefillArgs), vp]
     lib.arcb_decode.argtypes = [vp, i32, vp]
     lib.arcb_session_poll.argtypes = [vp, C.POINTER(i32), C.POINTER(i32), vp]
+    lib.arcb_session_attention_probe.argtypes = [vp, C.POINTER(C.c_float)]
+    lib.arcb_build_prompts.argtypes = [C.POINTER(PromptBuildArgs), vp]
+    lib.arcb_canonicalize_candidates.argtypes = [C.POINTER(CandidateArgs), vp]
     lib.arcb_launch_count.restype = i64
     lib.arcb_launch_count.argtypes = [C.c_int]
     lib.arcb_op_rmsnorm.argtypes = [vp, vp, vp, i32, i32, f32, i32, vp]

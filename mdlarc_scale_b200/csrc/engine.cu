@@ -93,6 +93,9 @@ struct arcb_session {
   cudaStream_t capture_stream = nullptr;
   long long graph_kernels = 0;
   bool armed = false;
+  // event pair recorded (as graph nodes) around the layer-0 decode-attention launch of every replay
+  cudaEvent_t probe_begin = nullptr, probe_end = nullptr;
+  bool probe_recorded = false;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -342,6 +345,10 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
   if (r != cudaSuccess) { delete s; return fail_cuda(r, "cudaMemset(session state)"); }
   r = cudaStreamCreateWithFlags(&s->capture_stream, cudaStreamNonBlocking);
   if (r != cudaSuccess) { delete s; return fail_cuda(r, "cudaStreamCreate"); }
+  if (cudaEventCreate(&s->probe_begin) != cudaSuccess || cudaEventCreate(&s->probe_end) != cudaSuccess) {
+    cudaGetLastError();
+    s->probe_begin = s->probe_end = nullptr;  // the probe is optional
+  }
   *out = s;
   return ARCB_OK;
 }
@@ -351,6 +358,8 @@ extern "C" int arcb_session_destroy(arcb_session* s) {
   if (s->graph_exec) cudaGraphExecDestroy(s->graph_exec);
   if (s->graph) cudaGraphDestroy(s->graph);
   if (s->capture_stream) cudaStreamDestroy(s->capture_stream);
+  if (s->probe_begin) cudaEventDestroy(s->probe_begin);
+  if (s->probe_end) cudaEventDestroy(s->probe_end);
   delete s;
   return ARCB_OK;
 }
@@ -405,7 +414,12 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
     aa.item_seq = seq; aa.item_len = kv_count; aa.item_skip = skip;
     aa.n_items = rows; aa.n_heads = c.n_heads; aa.t_max = T; aa.n_seqs = B;
     aa.n_splits = prefill ? 1 : s->splits; aa.scratch = s->attn_scratch; aa.act_f16 = f16; aa.err = e->d_err;
+    const bool probe = !prefill && l == 0 && s->probe_begin && s->probe_end;
+    // cudaEventRecordExternal: under stream capture this becomes an event-record NODE of the graph (a
+    // plain record would only mark a capture dependency and leave the event unusable for timing)
+    if (probe) CK(cudaEventRecordWithFlags(s->probe_begin, stream, cudaEventRecordExternal));
     CKL(arcb_launch_attn_stream(aa, stream), "attention");
+    if (probe) { CK(cudaEventRecordWithFlags(s->probe_end, stream, cudaEventRecordExternal)); s->probe_recorded = true; }
   }
 
   // out_proj + residual
@@ -535,6 +549,18 @@ extern "C" int arcb_session_poll(arcb_session* s, int32_t* n_finished, int32_t* 
     char buf[96];
     snprintf(buf, sizeof buf, "device error word = %d", err);
     return fail(ARCB_E_DEVICE, buf);
+  }
+  return ARCB_OK;
+}
+
+extern "C" int arcb_session_attention_probe(arcb_session* s, float* ms) {
+  if (!s || !ms) return fail(ARCB_E_ARG, "null argument");
+  if (!s->probe_recorded || !s->graph_exec) return fail(ARCB_E_STATE, "no decode step has run yet");
+  cudaError_t r = cudaEventSynchronize(s->probe_end);
+  if (r == cudaSuccess) r = cudaEventElapsedTime(ms, s->probe_begin, s->probe_end);
+  if (r != cudaSuccess) {
+    cudaGetLastError();  // a failed query must not be picked up by the next launch check
+    return fail_cuda(r, "attention probe");
   }
   return ARCB_OK;
 }

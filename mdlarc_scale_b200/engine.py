@@ -265,6 +265,12 @@ class Session:
         with torch.cuda.device(self.eng.device):
             _lib.check(self.eng.lib.arcb_decode(self._handle, int(n_steps), _stream_ptr(self.eng.device)))
 
+    def attention_probe_ms(self) -> float:
+        """Device time of the layer-0 decode-attention launch of the most recent decode step."""
+        ms = C.c_float(0)
+        _lib.check(self.eng.lib.arcb_session_attention_probe(self._handle, C.byref(ms)))
+        return float(ms.value)
+
     def poll(self) -> int:
         """Synchronise and return the number of rows that have emitted END; raises on a device error."""
         nf, err = C.c_int32(0), C.c_int32(0)

@@ -36,6 +36,8 @@ def main():
     ap.add_argument("--wave", type=int, default=1024)
     ap.add_argument("--embed-gain", type=float, default=8.0)
     ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--device-fanout", action="store_true",
+                    help="build prompts and canonical candidate records with the fan-out kernels")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -49,6 +51,8 @@ def main():
     cfg, sd = seeded_weights(args.size, 0, args.embed_gain)
     engine = Engine(sd, cfg, dev)
     tasks = synthetic.capped_tasks(args.seed, args.tasks, 2, 4, 1, args.hw_max, 2048)
+    if args.device_fanout:
+        return main_device_fanout(args, tasks, engine, rank, world, dev, dist)
     t0 = time.perf_counter()
     variants = sharding.enumerate_variants(tasks, num_color_perms=args.perms)
     t_enum = time.perf_counter() - t0
@@ -75,6 +79,40 @@ def main():
         print(json.dumps({
             "workload": f"{args.size}: {args.tasks} tasks x 8 dihedral x {args.perms} colour permutations",
             "n_gpus": world, "variants": len(variants), "max_new": args.max_new,
+            "enumerate_s": t_enum, "generate_and_gather_s": t_gen, "decode_grids_and_vote_s": t_vote,
+            "generated_tokens": gen_tokens, "generated_tokens_per_s": gen_tokens / t_gen,
+            "tasks_with_votes": sum(1 for v in votes.values() if v), "votes_sha256": digest}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main_device_fanout(args, tasks, engine, rank, world, dev, dist):
+    from . import fanout
+    t0 = time.perf_counter()
+    table = fanout.TaskTable(tasks, dev, num_color_perms=args.perms)
+    vt = table.variants()
+    t_enum = time.perf_counter() - t0
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    t1 = time.perf_counter()
+    records = sharding.generate_sharded_records(table, vt, args.max_new, rank, world, engine, wave_size=args.wave)
+    torch.cuda.synchronize(dev)
+    t_gen = time.perf_counter() - t1
+    t2 = time.perf_counter()
+    votes = fanout.vote_records(records, vt, top_k=2, seed=7)
+    t_vote = time.perf_counter() - t2
+    digest = hashlib.sha256(json.dumps(sorted((list(k), v) for k, v in votes.items())).encode()).hexdigest()
+    if dist is not None:
+        t = torch.tensor([t_gen], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_gen = float(t.item())
+    if rank == 0:
+        gen_tokens = int(fanout.record_fields(records)[4].astype(np.int64).sum())
+        print(json.dumps({
+            "workload": f"{args.size}: {args.tasks} tasks x 8 dihedral x {args.perms} colour permutations",
+            "fanout": "device", "n_gpus": world, "variants": len(vt), "max_new": args.max_new,
             "enumerate_s": t_enum, "generate_and_gather_s": t_gen, "decode_grids_and_vote_s": t_vote,
             "generated_tokens": gen_tokens, "generated_tokens_per_s": gen_tokens / t_gen,
             "tasks_with_votes": sum(1 for v in votes.values() if v), "votes_sha256": digest}), flush=True)

@@ -141,3 +141,59 @@ def engine_wave_fn(engine, stop_on_end: bool = True, max_prefill_tokens: int = 6
         sess.close()
 
     return run
+
+
+# ---------------------------------------------------------------------------
+# the same pipeline with the fan-out on the device (fanout.TaskTable): prompts are built by a
+# kernel from per-variant metadata, candidates leave as canonical records, and the records --
+# a quarter of the size of the token rows -- are what the all-gather carries
+# ---------------------------------------------------------------------------
+def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, engine, group=None,
+                             wave_size: int = 1024, stop_on_end: bool = True,
+                             max_prefill_tokens: int = 65536) -> np.ndarray:
+    """Generate this rank's variants and return every variant's candidate record in canonical
+    variant order (uint8 ``[len(vt), RECORD_BYTES]``, identical on all ranks)."""
+    from .fanout import RECORD_BYTES, check_status
+    dev = engine.device
+    n_var = len(vt)
+    per = rows_per_rank(n_var, world)
+    mine = assign(vt.length, world)[rank]
+    rec = torch.zeros((world * per, RECORD_BYTES), dtype=torch.uint8, device=dev)
+    local = rec[rank * per: (rank + 1) * per]
+    for w0 in range(0, len(mine), wave_size):
+        idx = mine[w0: w0 + wave_size]
+        n = len(idx)
+        lens = vt.length[idx]
+        tokens = torch.full((n, max_new), END_TOKEN_ID, dtype=torch.int32, device=dev)
+        cap = max(int(min(max_prefill_tokens, int(lens.sum()))), int(lens.max()), n)
+        sess = engine.new_session(n, int(lens.max()) + max_new, max_new, cap, stop_on_end=stop_on_end,
+                                  out_tokens=tokens)
+        plans, c0, tot = [], 0, 0
+        for i in range(n + 1):   # greedy split into prefill calls of at most `cap` packed tokens
+            if i == n or tot + int(lens[i]) > cap:
+                rows = np.arange(c0, i)
+                plans.append(table.build_prompts(vt, idx[rows], rows))
+                sess.prefill(plans[-1], None)
+                c0, tot = i, 0
+            if i < n:
+                tot += int(lens[i])
+        done = 0
+        while done < max_new - 1:
+            k = min(32, max_new - 1 - done)
+            sess.decode(k)
+            done += k
+            if stop_on_end and sess.poll() >= n:
+                break
+        sess.poll()
+        for p in plans:
+            check_status(p)
+        table.canonicalize(tokens, vt, idx, local[w0: w0 + n])   # straight into the gather slice
+        sess.close()
+    if world > 1:
+        import torch.distributed as dist
+        dist.all_gather_into_tensor(rec, local, group=group)
+    layout = gather_layout(vt.length, world)
+    valid = layout >= 0
+    out = np.zeros((n_var, RECORD_BYTES), np.uint8)
+    out[layout[valid]] = rec.cpu().numpy()[valid]
+    return out

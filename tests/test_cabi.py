@@ -38,6 +38,10 @@ def test_struct_sizes_match_c_layout():
     assert C.sizeof(_lib.Config) == 14 * 4
     assert C.sizeof(_lib.SessionDesc) == 128  # sizeof(arcb_session_desc) printed by a C compile of the header
     assert C.sizeof(_lib.PrefillArgs) == 176
+    assert C.sizeof(_lib.PromptBuildArgs) == 160
+    assert C.sizeof(_lib.CandidateArgs) == 96
+    from mdlarc_scale_b200 import fanout
+    assert fanout.RECORD_BYTES == 944 and fanout.MAX_CELLS == 936   # sizeof(arcb_candidate_record)
 
 
 def test_argument_errors_without_gpu(lib):

@@ -330,6 +330,26 @@ def test_bf16_activation_mode(golden_model):
     eng.close()
 
 
+def test_attention_probe_times_a_decode_step(golden_model):
+    """The event pair recorded inside the step graph reports a plausible time for one attention launch."""
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+    from mdlarc_scale_b200.engine import Engine, plan_prefill
+    cfg, sd = _weights("plain")
+    eng = Engine(sd, cfg, "cuda:0")
+    k = "plain_right"
+    ids, pos, mask = golden_model[k + "_ids"], golden_model[k + "_pos"], golden_model[k + "_mask"]
+    sess = eng.new_session(ids.shape[0], ids.shape[1] + 16, 16, 4096, stop_on_end=False)
+    import numpy as np
+    sess.prefill(plan_prefill(ids, pos, mask, np.arange(ids.shape[0])).to(torch.device("cuda:0")), None)
+    sess.decode(15)
+    sess.poll()
+    ms = sess.attention_probe_ms()
+    assert 0.0 < ms < 5.0, ms
+    sess.close()
+    eng.close()
+
+
 def test_argument_and_state_errors():
     """Error conventions of the boundary: bad mask shape, no room to generate, too-small buffers."""
     if not have_b200():
@@ -358,6 +378,8 @@ def test_argument_and_state_errors():
     assert b"kv cache too small" in lib.arcb_last_error()
     sess = eng.new_session(2, 64, 8, 128)
     assert lib.arcb_decode(sess._handle, 1, None) == _lib.E_STATE      # decode before any prefill
+    ms = C.c_float(0)
+    assert lib.arcb_session_attention_probe(sess._handle, C.byref(ms)) == _lib.E_STATE   # no step has run
     sess.close()
     with pytest.raises(NotImplementedError):
         Engine(sd, dict(vars(cfg), rope_type="1d"), "cuda:0")
