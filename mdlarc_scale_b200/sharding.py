@@ -189,11 +189,18 @@ def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, eng
             check_status(p)
         table.canonicalize(tokens, vt, idx, local[w0: w0 + n])   # straight into the gather slice
         sess.close()
+    return gather_records(rec, rank, world, vt.length, group)
+
+
+def gather_records(rec: torch.Tensor, rank: int, world: int, lengths, group=None) -> np.ndarray:
+    """Complete the gather buffer ``rec`` (``[world * per, width]``, this rank's slice filled) with ONE
+    in-place all-gather and return its rows in canonical variant order (host array)."""
+    per = rec.shape[0] // world
     if world > 1:
         import torch.distributed as dist
-        dist.all_gather_into_tensor(rec, local, group=group)
-    layout = gather_layout(vt.length, world)
+        dist.all_gather_into_tensor(rec, rec[rank * per: (rank + 1) * per], group=group)
+    layout = gather_layout(lengths, world)
     valid = layout >= 0
-    out = np.zeros((n_var, RECORD_BYTES), np.uint8)
+    out = np.zeros((len(lengths),) + tuple(rec.shape[1:]), rec.cpu().numpy().dtype)
     out[layout[valid]] = rec.cpu().numpy()[valid]
     return out

@@ -47,8 +47,23 @@ def _run(rank, world, port, out_path):
         layout = sharding.gather_layout([len(v.tokens) for v in variants], world)
         cands = sharding.candidates_from_tokens(variants, buf.numpy(), layout)
         votes = sharding.vote_all(tasks, cands, top_k=2, seed=3)
+        # the records pipeline: this rank's candidates as canonical records in its slice of the
+        # gather buffer (the CUDA path's kernel writes them; here the oracle does), one all-gather, vote
+        from mdlarc_scale_b200 import fanout
+        from oracle import arc_fanout
+        table = fanout.TaskTable(tasks, "cpu", num_color_perms=3)
+        vt = table.variants()
+        per = sharding.rows_per_rank(len(vt), world)
+        rec = torch.zeros((world * per, fanout.RECORD_BYTES), dtype=torch.uint8)
+        for j, v in enumerate(sharding.assign(vt.length, world)[rank].tolist()):
+            test_input = tasks[int(vt.task[v])]["test"][int(vt.test_idx[v])]["input"]
+            rec[rank * per + j] = torch.frombuffer(bytearray(arc_fanout.candidate_record(
+                buf[rank * per + j].tolist(), int(vt.dihedral[v]), table.perm_tuple(int(vt.perm[v])), test_input)),
+                dtype=torch.uint8)
+        records = sharding.gather_records(rec, rank, world, vt.length)
+        votes_rec = fanout.vote_records(records, vt, top_k=2, seed=3)
         with open(f"{out_path}.{rank}", "wb") as f:
-            pickle.dump((cands, votes), f)
+            pickle.dump((cands, votes, votes_rec), f)
     finally:
         dist.destroy_process_group()
 
@@ -84,6 +99,7 @@ def test_two_gloo_ranks_equal_single_process(tmp_path):
     mp.spawn(_run, args=(2, port, out), nprocs=2, join=True)
     for r in range(2):
         with open(f"{out}.{r}", "rb") as f:
-            cands, votes = pickle.load(f)
+            cands, votes, votes_rec = pickle.load(f)
         assert cands == want_c
         assert votes == want_v
+        assert votes_rec == want_v
