@@ -75,7 +75,11 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         t_gen = float(t.item())
     if rank == 0:
-        gen_tokens = int((buf != 13).sum().item()) + len(variants)
+        # tokens up to and including each row's first END (all of the row if it never ended)
+        has_end = (buf == 13).any(dim=1)
+        first_end = (buf == 13).int().argmax(dim=1)
+        gen_tokens = int(torch.where(has_end, first_end + 1, torch.full_like(first_end, buf.shape[1]))
+                         [torch.from_numpy(layout >= 0).to(buf.device)].sum().item())
         print(json.dumps({
             "workload": f"{args.size}: {args.tasks} tasks x 8 dihedral x {args.perms} colour permutations",
             "n_gpus": world, "variants": len(variants), "max_new": args.max_new,
