@@ -2,12 +2,14 @@
 
 Public API (same call signatures as the reference's ``src/inference.py`` / ``src/voting.py``):
 ``generate_output``, ``predict_with_augmentations``, ``forward_logits``, ``aaivr_predict``,
-``aggregate_votes``, ``compute_voting_stats``.
+``aggregate_votes``, ``compute_voting_stats``; and of ``src/eval.py``: ``evaluate_task``,
+``evaluate_dataset``, ``generate_submission``.
 """
 from .voting import aaivr_predict, aggregate_votes, compute_voting_stats, select_top_k  # noqa: F401
 
 __all__ = ["generate_output", "predict_with_augmentations", "forward_logits", "aaivr_predict",
-           "aggregate_votes", "compute_voting_stats", "select_top_k", "Engine"]
+           "aggregate_votes", "compute_voting_stats", "select_top_k", "Engine",
+           "evaluate_task", "evaluate_dataset", "generate_submission"]
 
 
 def __getattr__(name):  # torch-dependent parts are imported lazily
@@ -17,6 +19,9 @@ def __getattr__(name):  # torch-dependent parts are imported lazily
     if name in ("forward_logits", "B200TinyTransformer"):
         from . import transformer
         return getattr(transformer, name)
+    if name in ("evaluate_task", "evaluate_dataset", "generate_submission"):
+        from . import evaluation
+        return getattr(evaluation, name)
     if name in ("Engine", "engine_for"):
         from . import engine
         return getattr(engine, name)

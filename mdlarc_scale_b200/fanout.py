@@ -212,29 +212,42 @@ def record_fields(records: np.ndarray):
     return r[:, 0], r[:, 1], head[:, 1], head[:, 2], head[:, 3], r[:, 8:]
 
 
-def vote_records(records: np.ndarray, vt: VariantTable, top_k: int = 2, seed: int = 0,
-                 discard_input_copies: bool = True) -> dict:
-    """AAIVR top-k per (task, test_idx) from canonical records in variant order
-    (``records[i]`` belongs to variant ``i``).  Same tally, ordering and tie-break draws as
-    ``voting.aggregate_votes`` (src/voting.py:110-165) with the rng of ``sharding.vote_all``."""
+def tally_records(records: np.ndarray, vt: VariantTable, discard_input_copies: bool = True) -> dict:
+    """Per (task, test_idx): ``(ranked, n_total, n_valid)`` where ``ranked(rng)`` returns the
+    ``[(grid, votes), ...]`` list of ``voting.aggregate_votes`` (src/voting.py:110-165): same tally,
+    one ``rng.random()`` tie-break draw per distinct grid in first-seen order, votes descending.
+    ``records[i]`` belongs to variant ``i`` (canonical order)."""
     status, copy, hh, ww, _, cells = record_fields(records)
-    out: dict = {}
     n = len(vt)
+    out: dict = {}
     # variants of one (task, test) are contiguous in canonical order
     bounds = np.flatnonzero(np.diff(vt.template, prepend=-1, append=-1))
+    assert n == 0 or bounds[-1] == n
     for b0, b1 in zip(bounds[:-1].tolist(), bounds[1:].tolist()):
         tally: dict = {}
+        n_valid = 0
         for i in range(b0, b1):
             if status[i] != 1 or (discard_input_copies and copy[i]):
                 continue
+            n_valid += 1
             h, w = int(hh[i]), int(ww[i])
             key = (h, w, cells[i, : h * w].tobytes())
             tally[key] = tally.get(key, 0) + 1
-        ti, test_idx = int(vt.task[b0]), int(vt.test_idx[b0])
-        rng = random.Random(seed + 1000003 * ti + test_idx)
-        ranked = [(-votes, rng.random(), key) for key, votes in tally.items()]
-        ranked.sort(key=lambda r: (r[0], r[1]))
-        out[(ti, test_idx)] = [np.frombuffer(k[2], np.uint8).reshape(k[0], k[1]).tolist()
-                               for _, _, k in ranked[:top_k]]
-    assert n == 0 or bounds[-1] == n
+
+        def ranked(rng, tally=tally):
+            order = [(-votes, rng.random(), key) for key, votes in tally.items()]
+            order.sort(key=lambda r: (r[0], r[1]))
+            return [(np.frombuffer(k[2], np.uint8).reshape(k[0], k[1]).tolist(), -neg) for neg, _, k in order]
+
+        out[(int(vt.task[b0]), int(vt.test_idx[b0]))] = (ranked, b1 - b0, n_valid)
+    return out
+
+
+def vote_records(records: np.ndarray, vt: VariantTable, top_k: int = 2, seed: int = 0,
+                 discard_input_copies: bool = True) -> dict:
+    """AAIVR top-k per (task, test_idx) from canonical records, with the tie-break rng of
+    ``sharding.vote_all`` (``random.Random(seed + 1000003 * task + test_idx)``)."""
+    out = {}
+    for (ti, test_idx), (ranked, _, _) in tally_records(records, vt, discard_input_copies).items():
+        out[(ti, test_idx)] = [g for g, _ in ranked(random.Random(seed + 1000003 * ti + test_idx))[:top_k]]
     return out

@@ -36,6 +36,9 @@ def main():
     ap.add_argument("--wave", type=int, default=1024)
     ap.add_argument("--embed-gain", type=float, default=8.0)
     ap.add_argument("--seed", type=int, default=2)
+    ap.add_argument("--evaluate", action="store_true",
+                    help="run evaluate_dataset (variant sharding behind rank / world_size) and sum the "
+                         "per-rank counters as src/eval.py:1203-1208 does")
     ap.add_argument("--device-fanout", action="store_true",
                     help="build prompts and canonical candidate records with the fan-out kernels")
     args = ap.parse_args()
@@ -51,6 +54,8 @@ def main():
     cfg, sd = seeded_weights(args.size, 0, args.embed_gain)
     engine = Engine(sd, cfg, dev)
     tasks = synthetic.capped_tasks(args.seed, args.tasks, 2, 4, 1, args.hw_max, 2048)
+    if args.evaluate:
+        return main_evaluate(args, tasks, engine, rank, world, dev, dist)
     if args.device_fanout:
         return main_device_fanout(args, tasks, engine, rank, world, dev, dist)
     t0 = time.perf_counter()
@@ -86,6 +91,38 @@ def main():
             "enumerate_s": t_enum, "generate_and_gather_s": t_gen, "decode_grids_and_vote_s": t_vote,
             "generated_tokens": gen_tokens, "generated_tokens_per_s": gen_tokens / t_gen,
             "tasks_with_votes": sum(1 for v in votes.values() if v), "votes_sha256": digest}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main_evaluate(args, tasks, engine, rank, world, dev, dist):
+    from . import evaluation
+    challenges = {f"task{i:04d}": t for i, t in enumerate(tasks)}
+    # stand-in solutions (the synthetic tasks have none): the first train output of each task
+    solutions = {tid: [t["train"][0]["output"] for _ in t["test"]] for tid, t in challenges.items()}
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    t0 = time.perf_counter()
+    res = evaluation.evaluate_dataset(engine, challenges, dev, solutions=solutions, num_color_perms=args.perms,
+                                      top_k=2, max_output_tokens=args.max_new, show_progress=False, rank=rank,
+                                      world_size=world, vote_seed=7, wave_size=args.wave)
+    torch.cuda.synchronize(dev)
+    wall = time.perf_counter() - t0
+    fields = ["correct_at_1", "correct_at_2", "total_test_examples", "my_tasks", "arc_tasks_scored"]
+    counts = torch.tensor([res[f] for f in fields], dtype=torch.int64, device=dev)
+    outputs = {tid: tr["test_outputs"] for tid, tr in res["per_task_results"].items()}
+    if dist is not None:
+        dist.all_reduce(counts)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, outputs)
+        outputs = {k: v for part in gathered for k, v in part.items()}
+    if rank == 0:
+        digest = hashlib.sha256(json.dumps(sorted(outputs.items())).encode()).hexdigest()
+        print(json.dumps({"workload": f"evaluate_dataset, {args.size}: {args.tasks} tasks x 8 x {args.perms}",
+                          "n_gpus": world, "wall_s": wall, **dict(zip(fields, counts.tolist())),
+                          "tasks_reported": len(outputs), "outputs_sha256": digest}), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

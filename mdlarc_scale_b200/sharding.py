@@ -150,9 +150,18 @@ def engine_wave_fn(engine, stop_on_end: bool = True, max_prefill_tokens: int = 6
 # ---------------------------------------------------------------------------
 def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, engine, group=None,
                              wave_size: int = 1024, stop_on_end: bool = True,
-                             max_prefill_tokens: int = 65536) -> np.ndarray:
+                             max_prefill_tokens: int = 65536, example_ids=None, constraints: dict | None = None,
+                             temperature: float = 0.0, top_k: int = 0, sample_seed: int = 0,
+                             max_seq_len: int | None = None) -> np.ndarray:
     """Generate this rank's variants and return every variant's candidate record in canonical
-    variant order (uint8 ``[len(vt), RECORD_BYTES]``, identical on all ranks)."""
+    variant order (uint8 ``[len(vt), RECORD_BYTES]``, identical on all ranks).
+
+    ``example_ids`` (int array per variant) selects the example embedding of each sequence
+    (``None`` = no example embedding).  ``constraints`` holds per-variant ``palette_mask``
+    ``[n, 10]`` / ``target_shape`` ``[n, 2]`` arrays (either may be None) plus the scalar fields of
+    ``inference._constraints_dict``.  ``max_seq_len`` caps prompt + generated tokens of a wave
+    (src/inference.py:534-535, applied to the wave's longest prompt).
+    """
     from .fanout import RECORD_BYTES, check_status
     dev = engine.device
     n_var = len(vt)
@@ -164,22 +173,35 @@ def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, eng
         idx = mine[w0: w0 + wave_size]
         n = len(idx)
         lens = vt.length[idx]
-        tokens = torch.full((n, max_new), END_TOKEN_ID, dtype=torch.int32, device=dev)
+        new = max_new if max_seq_len is None else min(max_new, int(max_seq_len) - int(lens.max()))
+        if new <= 0:
+            continue   # no room to generate: these variants keep status 0 (no grid)
+        tokens = torch.full((n, new), END_TOKEN_ID, dtype=torch.int32, device=dev)
         cap = max(int(min(max_prefill_tokens, int(lens.sum()))), int(lens.max()), n)
-        sess = engine.new_session(n, int(lens.max()) + max_new, max_new, cap, stop_on_end=stop_on_end,
-                                  out_tokens=tokens)
+        wave_cons = None
+        if constraints is not None:
+            wave_cons = dict(constraints)
+            for key in ("palette_mask", "target_shape"):
+                if constraints.get(key) is not None:
+                    wave_cons[key] = np.ascontiguousarray(constraints[key][idx])
+        sess = engine.new_session(n, int(lens.max()) + new, new, cap, stop_on_end=stop_on_end,
+                                  out_tokens=tokens, constraints=wave_cons, temperature=temperature,
+                                  top_k=top_k, sample_seed=sample_seed + w0)
+        ex = None
+        if example_ids is not None:
+            ex = torch.from_numpy(np.ascontiguousarray(np.asarray(example_ids)[idx], dtype=np.int32)).to(dev)
         plans, c0, tot = [], 0, 0
         for i in range(n + 1):   # greedy split into prefill calls of at most `cap` packed tokens
             if i == n or tot + int(lens[i]) > cap:
                 rows = np.arange(c0, i)
                 plans.append(table.build_prompts(vt, idx[rows], rows))
-                sess.prefill(plans[-1], None)
+                sess.prefill(plans[-1], ex)
                 c0, tot = i, 0
             if i < n:
                 tot += int(lens[i])
         done = 0
-        while done < max_new - 1:
-            k = min(32, max_new - 1 - done)
+        while done < new - 1:
+            k = min(32, new - 1 - done)
             sess.decode(k)
             done += k
             if stop_on_end and sess.poll() >= n:

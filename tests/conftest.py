@@ -26,6 +26,11 @@ def golden_votes():
 
 
 @pytest.fixture(scope="session")
+def golden_eval():
+    return json.loads((GOLDEN / "eval.json").read_text())
+
+
+@pytest.fixture(scope="session")
 def golden_model():
     return dict(np.load(GOLDEN / "model_tiny.npz"))
 

@@ -7,7 +7,9 @@ Run where the reference source tree is available (it is imported read-only, neve
 Inputs are seeded; weights come from oracle.arc_model.init_state loaded into the reference's
 TinyTransformer with ``load_state_dict(strict=True)`` (so names and shapes are checked too).
 Outputs: model_tiny.npz (fp32 logits + greedy tokens), tokens.json (codec / position /
-augmentation known answers), votes.json (AAIVR results with seeded tie-break rngs).
+augmentation known answers), votes.json (AAIVR results with seeded tie-break rngs), eval.json
+(result dictionaries of the reference's evaluate_dataset / generate_submission for canned
+candidate lists).  ``--only NAME`` (tokens, votes, model, eval) rewrites one of them.
 """
 import json
 import random
@@ -187,8 +189,91 @@ def golden_votes():
     (HERE / "votes.json").write_text(json.dumps({"cases": cases}))
 
 
+def canned_predictions(task, test_idx, num_color_perms, solution):
+    """Candidate list of one test input, in the reference's order, with an unambiguous top two:
+    the true output wins for even test indices, a wrong grid for odd ones; noise has fewer votes."""
+    perms = rdata.generate_color_permutations(num_color_perms, seed=42)
+    rng = np.random.default_rng(1000 * len(task["train"]) + 17 * test_idx + len(solution))
+    wrong = [[(c + 1) % 10 for c in row] for row in solution]
+    noise = synthetic.random_grid(rng, 1, 4)
+    first, second = (solution, wrong) if test_idx % 2 == 0 else (wrong, solution)
+    if len(task["train"]) == 3:
+        second = noise          # noise outvotes the other attempt
+    if len(task["train"]) == 2:
+        first, second = wrong, noise   # a task with both attempts wrong
+    out = []
+    for d in range(8):
+        for p in range(num_color_perms):
+            perm = tuple(int(v) for v in perms[p]) if p > 0 else None
+            k = d * num_color_perms + p
+            g = first if k % 8 < 4 else second if k % 8 < 7 else noise
+            if k == 5:
+                out.append((None, d, perm))
+                continue
+            if k == 9:
+                out.append(([[1, 2], [3]], d, perm))
+                continue
+            if k == 11:
+                out.append(([list(r) for r in task["test"][test_idx]["input"]], 0, None))   # an input copy
+                continue
+            t = rdata.DIHEDRAL_TRANSFORMS[d](g)
+            if perm is not None:
+                t = [[perm[c] for c in row] for row in t]
+            out.append((t, d, perm))
+    return out
+
+
+def golden_eval():
+    import tempfile
+
+    from src import eval as reval
+    tasks = synthetic.capped_tasks(21, 5, 1, 3, 2, 5, None)
+    challenges, solutions = {}, {}
+    rng = np.random.default_rng(5)
+    for i, t in enumerate(tasks):
+        tid = f"task{(7 * i) % 5:02d}"
+        if i == 1:
+            t["test"].append({"input": synthetic.random_grid(rng, 2, 4)})
+        challenges[tid] = t
+        solutions[tid] = [synthetic.random_grid(rng, 2, 4) for _ in t["test"]]
+    del solutions["task01"][-1:]          # one task with a missing solution (unscored)
+    n_perms = 3
+
+    def fake_predict(model, task, test_idx, device, **kw):
+        tid = next(k for k, v in challenges.items() if v is task)
+        sol = solutions_full[tid][test_idx]
+        return canned_predictions(task, test_idx, kw["num_color_perms"], sol)
+
+    solutions_full = {k: list(v) for k, v in solutions.items()}
+    for tid, t in challenges.items():      # canned candidates need a target even where no solution is scored
+        while len(solutions_full[tid]) < len(t["test"]):
+            solutions_full[tid].append(synthetic.random_grid(rng, 2, 4))
+    reval.predict_with_augmentations = fake_predict
+
+    class Dummy(torch.nn.Module):
+        config = None
+
+    model = Dummy()
+    out = {"challenges": challenges, "solutions": solutions, "solutions_full": solutions_full, "num_color_perms": n_perms,
+           "dataset": {}}
+    for world in (1, 2):
+        for rank in range(world):
+            res = reval.evaluate_dataset(model, challenges, torch.device("cpu"), solutions=solutions,
+                                         num_color_perms=n_perms, top_k=2, show_progress=False, rank=rank,
+                                         world_size=world)
+            out["dataset"][f"{rank}/{world}"] = res
+    with tempfile.TemporaryDirectory() as tmp:
+        path = Path(tmp) / "sub" / "submission.json"
+        reval.generate_submission(model, challenges, path, torch.device("cpu"), num_color_perms=n_perms,
+                                  show_progress=False)
+        out["submission"] = json.loads(path.read_text())
+    (HERE / "eval.json").write_text(json.dumps(out))
+
+
 if __name__ == "__main__":
-    golden_tokens()
-    golden_votes()
-    golden_model()
+    only = sys.argv[sys.argv.index("--only") + 1] if "--only" in sys.argv else None
+    for name, fn in (("tokens", golden_tokens), ("votes", golden_votes), ("model", golden_model),
+                     ("eval", golden_eval)):
+        if only in (None, name):
+            fn()
     print("golden fixtures written to", HERE)
