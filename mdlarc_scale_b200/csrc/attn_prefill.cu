@@ -6,10 +6,11 @@
 //   TMA        K and V tiles [128 keys][64 dims], 128-byte swizzle, 3-stage ring shared by A and B
 //   MMA        S_x = Q_x K^T   (UMMA 128x128x16 x4, fp32 in TMEM)            x in {A, B}
 //   softmax_x  the row's 128 scores are read once from TMEM into registers; row max;
-//              p = exp2(s*c - m_ref) written 16-bit into shared memory in the swizzled K-major
-//              layout the MMA reads
-//   MMA        O_x += P_x V    (UMMA 128x64x16 x8, V is the MN-major B operand), accumulated in
-//              TMEM across all tiles
+//              p = exp2(s*c - m_ref) written 16-bit back into TMEM (64 columns per Q tile: the
+//              A operand of the next product is read from tensor memory, so P never touches
+//              shared memory)
+//   MMA        O_x += P_x V    (UMMA 128x64x16 x8, A = P from TMEM, V is the MN-major B operand),
+//              accumulated in TMEM across all tiles
 // The reference maximum m_ref of a row is only raised when the true maximum exceeds it by more
 // than 8 (in log2 units), so p <= 256 stays well inside the 16-bit range and the accumulated O
 // rarely needs rescaling; when it does, the row's thread rescales O in TMEM before releasing P.
@@ -29,10 +30,11 @@ namespace {
 constexpr int BQ = 128, BKV = 128, HD = 64;
 constexpr int Q_BYTES = BQ * HD * 2;          // 16 KB per Q tile
 constexpr int KV_TILE_BYTES = BKV * HD * 2;   // 16 KB each for K and V
-constexpr int P_BYTES = BQ * BKV * 2;         // 32 KB per Q tile: two [128][64] swizzled K-major tiles
-constexpr int KV_STAGES = 3;
-constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 2 * P_BYTES + 1024 + 256;
-constexpr int TMEM_COLS = 512;  // S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384)
+constexpr int KV_STAGES = 4;
+constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 1024 + 256;
+// S_A [0,128) S_B [128,256) O_A [256,320) O_B [320,384) P_A [384,448) P_B [448,512)
+constexpr int TMEM_COLS = 512;
+constexpr int TMEM_P = 384;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int N_THREADS = 320;
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
@@ -90,9 +92,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   uint8_t* base_ptr = smem_raw + (base - raw);
   const uint32_t q_smem = base;                                   // tile x at + x * Q_BYTES
   const uint32_t kv_smem = base + 2 * Q_BYTES;                    // stage s: K at + s*32K, V at +16K
-  const uint32_t p_smem = kv_smem + KV_STAGES * 2 * KV_TILE_BYTES;  // tile x at + x * P_BYTES
-  uint8_t* p_ptr = base_ptr + 2 * Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES;
-  const uint32_t bar0 = p_smem + 2 * P_BYTES;
+  const uint32_t bar0 = kv_smem + KV_STAGES * 2 * KV_TILE_BYTES;
+  uint8_t* bar_ptr = base_ptr + 2 * Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES;
   Bars B;
   B.q = bar0;
   B.kv_full = bar0 + 8;                  // KV_STAGES barriers
@@ -105,7 +106,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   B.o[1] = B.s[0] + 40;
   B.sfree[0] = B.s[0] + 48;
   B.sfree[1] = B.s[0] + 56;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(p_ptr + 2 * P_BYTES + 128);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_ptr + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int blk = blockIdx.x, h = blockIdx.y;
@@ -193,9 +194,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const uint32_t d_o = tmem_base + 256 + x * 64;
 #pragma unroll
         for (int ks = 0; ks < BKV / 16; ++ks) {
-          const uint64_t dp = umma_desc_k_sw128(p_smem + x * P_BYTES + (ks >> 2) * (BQ * 128)) + 2 * (ks & 3);
+          // A = P_x from tensor memory: 16 keys = 8 columns of packed 16-bit pairs;
           // 16 keys = 16 rows of 128 bytes = 2048 bytes further into the V tile
-          umma_f16(d_o, dp, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv, (j | ks) ? 1u : 0u);
+          umma_f16_ts(d_o, tmem_base + TMEM_P + x * 64 + ks * 8, dv + (uint64_t)(ks * (2048 >> 4)), idesc_pv,
+                      (j | ks) ? 1u : 0u);
         }
         umma_commit(B.o[x]);
       };
@@ -242,7 +244,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t t_lane = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const uint32_t t_s = t_lane + grp * 128;
     const uint32_t t_o = t_lane + 256 + grp * 64;
-    uint8_t* p_row = p_ptr + grp * P_BYTES + r * 128;
+    const uint32_t t_p = t_lane + TMEM_P + grp * 64;
     const float sc = 0.125f * LOG2E;
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
@@ -333,17 +335,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           const __half2 t = __hadd2(__hadd2(__hadd2(p[0], p[1]), __hadd2(p[2], p[3])),
                                     __hadd2(__hadd2(p[4], p[5]), __hadd2(p[6], p[7])));
           lsum += __low2float(t) + __high2float(t);
-          // columns [16 g, 16 g + 16): P sub-tile g / 4, chunks 2 (g % 4) and 2 (g % 4) + 1
-          uint8_t* tile = p_row + (g >> 2) * (BQ * 128);
-          const int ch0 = (g & 3) * 2;
 #pragma unroll
-          for (int q = 0; q < 2; ++q) {
-            const int ch = (ch0 + q) ^ (r & 7);
-            *reinterpret_cast<uint4*>(tile + ch * 16) =
-                make_uint4(h2_bits(p[4 * q]), h2_bits(p[4 * q + 1]), h2_bits(p[4 * q + 2]), h2_bits(p[4 * q + 3]));
-          }
+          for (int e = 0; e < 8; ++e) h2[g * 8 + e] = p[e];   // keys 16 g .. 16 g + 15 = P columns 8 g .. 8 g + 7
         }
         l += lsum;
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t pk[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) pk[i] = h2_bits(h2[c * 32 + i]);
+          tmem_st_32x32(t_p + c * 32, pk);
+        }
       } else {
         // the row's 128 scores, read once
         uint32_t sv[4][32];
@@ -407,36 +409,30 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
         float ls0 = 0.f, ls1 = 0.f;
-        // probabilities -> shared memory (swizzled K-major, 16-bit)
+        // probabilities -> tensor memory (16-bit pairs, 16 columns per 32 keys)
   #pragma unroll
-        for (int c = 0; c < BKV / 32; ++c) {
-          uint32_t pk[16];
+        for (int c = 0; c < BKV / 32; c += 2) {
+          uint32_t pk[32];
+  #pragma unroll
+          for (int cc = 0; cc < 2; ++cc)
   #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            float p0 = ex2_fast(fmaf(__uint_as_float(sv[c][i]), sc, -m_safe));
-            float p1 = ex2_fast(fmaf(__uint_as_float(sv[c][i + 1]), sc, -m_safe));
+            float p0 = ex2_fast(fmaf(__uint_as_float(sv[c + cc][i]), sc, -m_safe));
+            float p1 = ex2_fast(fmaf(__uint_as_float(sv[c + cc][i + 1]), sc, -m_safe));
             if (!full) {
-              if (c * 32 + i >= n_valid) p0 = 0.f;
-              if (c * 32 + i + 1 >= n_valid) p1 = 0.f;
+              if ((c + cc) * 32 + i >= n_valid) p0 = 0.f;
+              if ((c + cc) * 32 + i + 1 >= n_valid) p1 = 0.f;
             }
             ls0 += p0;
             ls1 += p1;
-            pk[i >> 1] = pack2_prob(p0, p1, a.act_f16);
+            pk[cc * 16 + (i >> 1)] = pack2_prob(p0, p1, a.act_f16);
           }
-          // columns [c*32, c*32+32) of row r: tile = c / 2, 16-byte chunks ch0 .. ch0+3
-          uint8_t* tile = p_row + (c >> 1) * (BQ * 128);
-          const int ch0 = (c & 1) * 4;
-  #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const int ch = (ch0 + q4) ^ (r & 7);
-            *reinterpret_cast<uint4*>(tile + ch * 16) =
-                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-          }
+          tmem_st_32x32(t_p + (c >> 1) * 32, pk);
         }
         l += ls0 + ls1;
       }
-      // make the generic-proxy writes of P visible to the tensor-core (async) proxy
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      // P is complete in tensor memory before the MMA warp is told
+      tmem_wait_st();
       tc_fence_before();
       mbar_arrive(B.p[grp]);
     }

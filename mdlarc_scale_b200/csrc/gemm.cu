@@ -33,6 +33,57 @@ struct TcCfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
 };
 
+// The residual epilogue stages 128 x 32 fp32 chunks in shared memory (one 16 KB buffer per group of
+// four epilogue warps) and adds them to the residual stream with a bulk tensor reduce.
+constexpr int EPI_STAGE_GROUP_BYTES = 128 * 32 * 4;
+template <int MODE>
+__host__ __device__ constexpr int epi_stage_bytes() { return MODE == EPI_RESID ? 2 * EPI_STAGE_GROUP_BYTES : 0; }
+
+// Residual epilogue: x[m][n] += acc[m][n] (+ bias[n]) for this CTA's 128 rows and this group's
+// column half, 32 columns at a time.  Each thread drops its row's 32 values into the staging
+// buffer (128-byte rows, 16-byte chunks XOR-swizzled by row like the TMA 128-byte swizzle, so the
+// row-per-thread writes are conflict-free), and one thread issues a bulk tensor reduce-add of the
+// 128 x 32 box: the addition happens in L2 on whole sectors, rows beyond M are clipped by the
+// tensor map, and every element of x receives exactly one addend per GEMM, so the result is the
+// same fp32 sum a load-add-store would give.  The group's four warps meet at named barrier
+// 1 + col_half; `elected` is the thread that owns the bulk groups.
+template <int BN>
+__device__ __forceinline__ void epilogue_resid_tma(const GemmEpilogue& ep, const CUtensorMap* tmap_x, uint32_t t_row,
+                                                   int m0, int n_tile0, int col_half, int row_in_tile,
+                                                   uint32_t stage_smem, uint8_t* stage_ptr, bool elected) {
+  uint8_t* my_row = stage_ptr + row_in_tile * 128;
+  const int sw = row_in_tile & 7;
+#pragma unroll 1
+  for (int c = col_half * (BN / 64); c < (col_half + 1) * (BN / 64); ++c) {
+    const int n0 = n_tile0 + c * 32;
+    if (n0 >= ep.N) break;  // uniform over the group
+    uint32_t r[32];
+    tmem_ld_32x32(t_row + c * 32, r);
+    tmem_wait_ld();
+    if (ep.bias) {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float4 b = __ldg(reinterpret_cast<const float4*>(ep.bias + n0 + 4 * q));
+        r[4 * q] = __float_as_uint(__uint_as_float(r[4 * q]) + b.x);
+        r[4 * q + 1] = __float_as_uint(__uint_as_float(r[4 * q + 1]) + b.y);
+        r[4 * q + 2] = __float_as_uint(__uint_as_float(r[4 * q + 2]) + b.z);
+        r[4 * q + 3] = __float_as_uint(__uint_as_float(r[4 * q + 3]) + b.w);
+      }
+    }
+    if (elected) bulk_wait_read_all();        // the previous reduce has read the buffer
+    named_bar_sync(1 + col_half, 128);
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<uint4*>(my_row + ((q ^ sw) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+    fence_proxy_async_smem();
+    named_bar_sync(1 + col_half, 128);
+    if (elected && m0 < ep.M) {
+      tma_reduce_add_2d(tmap_x, stage_smem, n0, m0);
+      bulk_commit_group();
+    }
+  }
+}
+
 // Drains one accumulator tile (this thread's row, the 32-column chunks of its column half) from
 // TMEM through the epilogue MODE.  t_row: TMEM address of the row's first accumulator column;
 // n_tile0: first output column of the tile.  tcgen05.ld is warp-collective, so every lane runs the
@@ -104,18 +155,21 @@ __device__ __forceinline__ void epilogue_tile(const GemmEpilogue& ep, uint32_t t
 template <int BN, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               GemmEpilogue ep, int K, uint32_t idesc, int tiles_n, int tiles_total) {
+               const __grid_constant__ CUtensorMap tmap_x, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
+               int tiles_total) {
   using Cfg = TcCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
-  const uint32_t bar_base = base + Cfg::STAGES * Cfg::STAGE_BYTES;
+  // operand stages | residual staging (EPI_RESID only) | barriers
+  constexpr int RING_BYTES = Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = base + RING_BYTES + epi_stage_bytes<MODE>();
   // full[s] at +8s, empty[s] at +8(STAGES+s), acc_full[2], acc_empty[2] after them
   const uint32_t bar_acc_full = bar_base + 16 * Cfg::STAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 16;
-  volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 16 * Cfg::STAGES + 32);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      base_ptr + RING_BYTES + epi_stage_bytes<MODE>() + 16 * Cfg::STAGES + 32);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,6 +188,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (MODE == EPI_RESID) tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
@@ -220,15 +275,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const bool row_ok = m < ep.M;
       bool ok = mbar_wait_bounded(bar_acc_full + 8 * acc, (it >> 1) & 1);
       if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-      ok = __all_sync(0xffffffffu, ok);
+      // the four warps of a group share named barriers below, so they must leave together
+      if constexpr (MODE == EPI_RESID) ok = !named_bar_or(1 + col_half, 128, !ok);
+      else ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
+      if constexpr (MODE == EPI_RESID)
+        epilogue_resid_tma<BN>(ep, &tmap_x, t_row, m_blk * TC_BM, n_blk * BN, col_half, row_in_tile,
+                               base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
+                               base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      else
+        epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained: hand it back to the MMA warp
       tc_fence_before();
       mbar_arrive(bar_acc_empty + 8 * acc);
     }
+    if (MODE == EPI_RESID && quarter == 0 && lane == 0) bulk_wait_all();  // reduces done before the CTA exits
   }
   tc_fence_before();
   __syncthreads();
@@ -262,18 +325,21 @@ struct Tc2Cfg {
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                GemmEpilogue ep, int K, uint32_t idesc, int tiles_n, int tiles_total) {
+                const __grid_constant__ CUtensorMap tmap_x, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
+                int tiles_total) {
   using Cfg = Tc2Cfg;
   constexpr int BN = Cfg::BN;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
-  const uint32_t bar_base = base + Cfg::STAGES * Cfg::STAGE_BYTES;
+  // operand stages | residual staging (EPI_RESID only) | barriers; the same offsets in both CTAs
+  constexpr int RING_BYTES = Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = base + RING_BYTES + epi_stage_bytes<MODE>();
   const uint32_t bar_acc_full = bar_base + 16 * Cfg::STAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 16;
-  volatile uint32_t* tmem_slot =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + Cfg::STAGES * Cfg::STAGE_BYTES + 16 * Cfg::STAGES + 32);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      base_ptr + RING_BYTES + epi_stage_bytes<MODE>() + 16 * Cfg::STAGES + 32);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -294,6 +360,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (MODE == EPI_RESID) tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
     tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
@@ -378,16 +445,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const bool row_ok = m < ep.M;
       bool ok = mbar_wait_bounded(bar_acc_full + 8 * acc, (it >> 1) & 1);
       if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-      ok = __all_sync(0xffffffffu, ok);
+      if constexpr (MODE == EPI_RESID) ok = !named_bar_or(1 + col_half, 128, !ok);
+      else ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
-      epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
+      if constexpr (MODE == EPI_RESID)
+        epilogue_resid_tma<BN>(ep, &tmap_x, t_row, m_blk * 256 + (int)rank * 128, n_blk * BN, col_half, row_in_tile,
+                               base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
+                               base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      else
+        epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained by this warp: tell the leader's MMA thread
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cta0(bar_acc_empty + 8 * acc);
     }
+    if (MODE == EPI_RESID && quarter == 0 && lane == 0) bulk_wait_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -516,6 +590,19 @@ int arcb_make_tmap_2d_16b(CUtensorMap* out, const void* ptr, uint64_t rows, uint
   return (int)r;
 }
 
+// fp32 [rows][cols] tensor with 128 x 32 boxes (128-byte rows, 128-byte swizzle): the residual stream
+static int make_tmap_resid_f32(CUtensorMap* out, float* ptr, uint64_t rows, uint64_t cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -100;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {cols * 4};
+  cuuint32_t box[2] = {32, 128};
+  cuuint32_t estr[2] = {1, 1};
+  return (int)fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, gdim, gstride, box, estr,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+}
+
 bool arcb_gemm_tc_supported(int M, int N, int K) {
   (void)M;
   return (N % 128 == 0) && (K % 64 == 0) && K >= 64;
@@ -524,10 +611,10 @@ bool arcb_gemm_tc_supported(int M, int N, int K) {
 template <int MODE>
 static cudaError_t set_tc_smem_attr() {
   cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<128, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       TcCfg<128>::SMEM_BYTES);
+                                       TcCfg<128>::SMEM_BYTES + epi_stage_bytes<MODE>());
   if (e != cudaSuccess) return e;
   return cudaFuncSetAttribute(gemm_tc_kernel<256, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              TcCfg<256>::SMEM_BYTES);
+                              TcCfg<256>::SMEM_BYTES + epi_stage_bytes<MODE>());
 }
 
 static int g_num_sms = 0;
@@ -535,7 +622,8 @@ static int g_max_pairs = 0;  // 2-CTA clusters that can be resident at once
 
 template <int MODE>
 static cudaError_t set_tc2_smem_attr() {
-  return cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Tc2Cfg::SMEM_BYTES);
+  return cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>());
 }
 
 // Opt in to the large dynamic shared memory of every tcgen05 instantiation (call once, outside
@@ -554,7 +642,7 @@ int arcb_gemm_init() {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148);
     cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = Tc2Cfg::SMEM_BYTES;
+    cfg.dynamicSmemBytes = Tc2Cfg::SMEM_BYTES + epi_stage_bytes<EPI_RESID>();
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
@@ -571,24 +659,25 @@ int arcb_gemm_init() {
 }
 
 template <int BN, int MODE>
-static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue& ep, int K, int act_f16,
-                      cudaStream_t stream) {
+static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const GemmEpilogue& ep,
+                      int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + BN - 1) / BN, tiles_m = (ep.M + TC_BM - 1) / TC_BM;
   const int tiles = tiles_n * tiles_m;
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
   const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
-  gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, TC_THREADS, TcCfg<BN>::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc,
-                                                                                            tiles_n, tiles);
+  gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, TC_THREADS, TcCfg<BN>::SMEM_BYTES + epi_stage_bytes<MODE>(),
+                             stream>>>(ta, tb, tx, ep, K, idesc, tiles_n, tiles);
 }
 
 template <int MODE>
-static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const GemmEpilogue& ep, int K, int act_f16,
-                       cudaStream_t stream) {
+static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const GemmEpilogue& ep,
+                       int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + 255) / 256, tiles_m = (ep.M + 255) / 256;
   const int tiles = tiles_n * tiles_m;
   const int pairs = tiles < g_max_pairs ? tiles : g_max_pairs;
   const uint32_t idesc = umma_idesc_f16(256, 256, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
-  gemm_tc2_kernel<MODE><<<2 * pairs, TC_THREADS, Tc2Cfg::SMEM_BYTES, stream>>>(ta, tb, ep, K, idesc, tiles_n, tiles);
+  gemm_tc2_kernel<MODE><<<2 * pairs, TC_THREADS, Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>(), stream>>>(
+      ta, tb, tx, ep, K, idesc, tiles_n, tiles);
 }
 
 int arcb_gemm_max_pairs() { return g_max_pairs; }
@@ -610,9 +699,14 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
     if (r) return 1000 + r;
     r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, (wide && !pair) ? 256 : 128, TC_BK, act_f16);
     if (r) return 1000 + r;
-    if (pair) launch_tc2<MODE>(ta, tb, ep, K, act_f16, stream);
-    else if (wide) launch_tc<256, MODE>(ta, tb, ep, K, act_f16, stream);
-    else launch_tc<128, MODE>(ta, tb, ep, K, act_f16, stream);
+    CUtensorMap tx = ta;  // only the residual epilogue reads it
+    if (MODE == EPI_RESID) {
+      r = make_tmap_resid_f32(&tx, ep.x, (uint64_t)M, (uint64_t)N);
+      if (r) return 1000 + r;
+    }
+    if (pair) launch_tc2<MODE>(ta, tb, tx, ep, K, act_f16, stream);
+    else if (wide) launch_tc<256, MODE>(ta, tb, tx, ep, K, act_f16, stream);
+    else launch_tc<128, MODE>(ta, tb, tx, ep, K, act_f16, stream);
   } else {
     dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
     gemm_simt_kernel<MODE><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a16),
