@@ -134,3 +134,20 @@ def test_vote_from_records_equals_vote_from_tokens():
         o = arc_vote.aaivr_predict(preds, 3, tasks[ti]["test"][te]["input"], discard_input_copies=False,
                                    rng=random.Random(1 + 1000003 * ti + te))
         assert keep[(ti, te)] == o
+
+
+def test_tally_of_empty_and_invalid_groups():
+    """No valid candidate for a test input gives an empty vote (tests/test_voting.py:194-233)."""
+    tasks = _tasks(seed=9, n=3)
+    table = fanout.TaskTable(tasks, "cpu", num_color_perms=2)
+    vt = table.variants()
+    rows = make_generations(tasks, table, vt, 32, seed=1)
+    rec = host_records(tasks, table, vt, rows)
+    first = vt.template == 0
+    rec[first, 0] = np.where(np.arange(first.sum()) % 2 == 0, 0, 2)     # nothing / malformed only
+    tallies = fanout.tally_records(rec, vt)
+    ranked, n_total, n_valid = tallies[(0, 0)]
+    assert ranked(random.Random(0)) == [] and n_total == 16 and n_valid == 0
+    assert fanout.vote_records(rec, vt)[(0, 0)] == []
+    assert fanout.vote_records(np.zeros((0, fanout.RECORD_BYTES), np.uint8),
+                               fanout.TaskTable([], "cpu").variants()) == {}
