@@ -224,6 +224,13 @@ int arcb_op_rmsnorm(const float* d_x, const float* d_w, void* d_out16, int32_t r
 int arcb_op_gemm(const void* d_a16, const void* d_w16, float* d_y, int32_t M, int32_t N,
                  int32_t K, int32_t act_format, int32_t gemm_path, void* stream);
 
+/* x[M,N] (fp32, in place) += A[M,K] * W[N,K]^T (+ bias[N], may be NULL): a linear layer followed by
+ * the residual add, as out_proj at src/inference.py:410-412 / 453-455 and the FFN's down projection
+ * at src/transformer.py:446-451 with src/inference.py:413 / 456.  The tensor-core kernels add through
+ * a bulk tensor reduce; every element receives one addend, so the result is deterministic. */
+int arcb_op_gemm_residual(const void* d_a16, const void* d_w16, const float* d_bias, float* d_x, int32_t M,
+                          int32_t N, int32_t K, int32_t act_format, int32_t gemm_path, void* stream);
+
 /* Attention of one query vector per item over a cached K/V prefix:
  * F.scaled_dot_product_attention at src/inference.py:452 (is_causal=False, key mask
  * expressed as a length).  q16/out16: [n_items][H][64]; K, V: [B][H][t_max][64] bf16;

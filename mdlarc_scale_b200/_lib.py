@@ -27,6 +27,7 @@ EXPORTS = [
     "arcb_engine_load_tensor", "arcb_session_workspace_bytes", "arcb_kv_cache_bytes",
     "arcb_session_create", "arcb_session_destroy", "arcb_prefill", "arcb_decode",
     "arcb_session_poll", "arcb_session_attention_probe", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
+    "arcb_op_gemm_residual",
     "arcb_attn_scratch_bytes", "arcb_op_decode_attention", "arcb_op_decode_attention_static",
     "arcb_op_head", "arcb_build_prompts", "arcb_canonicalize_candidates",
 ]
@@ -135,6 +136,7 @@ def load() -> C.CDLL:
     lib.arcb_launch_count.argtypes = [C.c_int]
     lib.arcb_op_rmsnorm.argtypes = [vp, vp, vp, i32, i32, f32, i32, vp]
     lib.arcb_op_gemm.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.arcb_op_gemm_residual.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.arcb_attn_scratch_bytes.restype = i64
     lib.arcb_attn_scratch_bytes.argtypes = [i32, i32, i32]
     lib.arcb_op_decode_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]

@@ -593,6 +593,24 @@ extern "C" int arcb_op_gemm(const void* a16, const void* w, float* y, int32_t M,
   return ARCB_OK;
 }
 
+extern "C" int arcb_op_gemm_residual(const void* a16, const void* w, const float* bias, float* x, int32_t M,
+                                     int32_t N, int32_t K, int32_t act_format, int32_t gemm_path, void* stream) {
+  if (!a16 || !w || !x || M <= 0) return fail(ARCB_E_ARG, "bad gemm arguments");
+  static bool inited = false;
+  if (!inited) { CKL(arcb_gemm_init(), "gemm init"); inited = true; }
+  if (N % 128 || K % 32) return fail(ARCB_E_ARG, "gemm needs N % 128 == 0 and K % 32 == 0");
+  const int variant = gemm_path == ARCB_GEMM_TC_1CTA ? 1 : (gemm_path == ARCB_GEMM_TC_2CTA ? 2 : 0);
+  bool tc = gemm_path == ARCB_GEMM_TC || variant != 0 || (gemm_path == ARCB_GEMM_AUTO && M > 32);
+  if (tc && !arcb_gemm_tc_supported(M, N, K)) {
+    if (gemm_path != ARCB_GEMM_AUTO) return fail(ARCB_E_ARG, "tcgen05 gemm needs K % 64 == 0");
+    tc = false;
+  }
+  GemmEpilogue ep{};
+  ep.mode = EPI_RESID; ep.M = M; ep.N = N; ep.x = x; ep.bias = bias;
+  CKL(arcb_launch_gemm(a16, w, ep, K, act_format == ARCB_ACT_F16, tc, (cudaStream_t)stream, variant), "gemm");
+  return ARCB_OK;
+}
+
 extern "C" int64_t arcb_attn_scratch_bytes(int32_t n_items, int32_t n_heads, int32_t n_splits) {
   if (n_items <= 0 || n_heads <= 0 || n_splits <= 1) return 0;
   return (int64_t)n_items * n_heads * n_splits * ATTN_SCRATCH_STRIDE * 4;

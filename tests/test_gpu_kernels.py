@@ -48,6 +48,32 @@ def test_gemm(lib, path, fmt, M, N, K):
     assert err < 2e-4 * math.sqrt(K / 64), f"max abs err {err}"
 
 
+@pytest.mark.parametrize("path", [_lib.GEMM_SIMT, _lib.GEMM_TC_1CTA, _lib.GEMM_TC_2CTA], ids=["simt", "tc1cta", "tc2cta"])
+@pytest.mark.parametrize("with_bias", [False, True])
+@pytest.mark.parametrize("M,N,K", [(33, 256, 128), (129, 384, 704), (300, 1280, 256), (1000, 1280, 3392),
+                                   (1024, 768, 768), (20001, 1280, 192)])
+def test_gemm_residual(lib, path, with_bias, M, N, K):
+    """x += A W^T (+ bias): the residual epilogue (bulk tensor reduce on the tensor-core kernels),
+    row counts that leave a partial last tile, bitwise identical when repeated."""
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = to_act(torch.randn(M, K, device="cuda", generator=g), _lib.ACT_F16)
+    w = to_act((torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16).float(), _lib.ACT_F16)
+    bias = torch.randn(N, device="cuda", generator=g) if with_bias else None
+    x0 = torch.randn(M + 3, N, device="cuda", generator=g)     # three guard rows after the last one
+    outs = []
+    for _ in range(2):
+        x = x0.clone()
+        _lib.check(lib.arcb_op_gemm_residual(a.data_ptr(), w.data_ptr(), bias.data_ptr() if with_bias else None,
+                                             x.data_ptr(), M, N, K, _lib.ACT_F16, path, stream()))
+        torch.cuda.synchronize()
+        outs.append(x)
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0][M:], x0[M:])                    # rows beyond M are untouched
+    ref = x0[:M].double() + a.double() @ w.double().t() + (bias.double() if with_bias else 0.0)
+    err = (outs[0][:M].double() - ref).abs().max().item()
+    assert err < 2e-4 * math.sqrt(K / 64) + 1e-5, f"max abs err {err}"
+
+
 @pytest.mark.parametrize("splits", [1, 4, 7])
 @pytest.mark.parametrize("fmt", [_lib.ACT_F16, _lib.ACT_BF16])
 def test_decode_attention(lib, splits, fmt):
