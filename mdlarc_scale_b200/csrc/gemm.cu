@@ -37,7 +37,12 @@ struct TcCfg {
 // four epilogue warps) and adds them to the residual stream with a bulk tensor reduce.
 constexpr int EPI_STAGE_GROUP_BYTES = 128 * 32 * 4;
 template <int MODE>
-__host__ __device__ constexpr int epi_stage_bytes() { return MODE == EPI_RESID ? 2 * EPI_STAGE_GROUP_BYTES : 0; }
+__host__ __device__ constexpr int epi_stage_bytes() {
+  return (MODE == EPI_RESID || MODE == EPI_SWIGLU) ? 2 * EPI_STAGE_GROUP_BYTES : 0;
+}
+// epilogues that go through the staging buffers and the third tensor map
+template <int BN, int MODE>
+__host__ __device__ constexpr bool epi_staged() { return MODE == EPI_RESID || (MODE == EPI_SWIGLU && BN == 256); }
 
 // Residual epilogue: x[m][n] += acc[m][n] (+ bias[n]) for this CTA's 128 rows and this group's
 // column half, 32 columns at a time.  Each thread drops its row's 32 values into the staging
@@ -81,6 +86,55 @@ __device__ __forceinline__ void epilogue_resid_tma(const GemmEpilogue& ep, const
       tma_reduce_add_2d(tmap_x, stage_smem, n0, m0);
       bulk_commit_group();
     }
+  }
+}
+
+// SwiGLU epilogue of one 128-column accumulator group (64 gate columns, then the matching 64 up
+// columns) of a 256-column tile: h[m][j] = silu(g + bg) * (u + bu) for the group's 64 outputs.  The
+// group's four warps stage the 128 x 64 16-bit box (128-byte rows, XOR-swizzled 16-byte chunks) and
+// one thread issues a bulk tensor store, instead of 8-byte stores a row pitch apart.
+__device__ __forceinline__ void epilogue_swiglu_tma(const GemmEpilogue& ep, const CUtensorMap* tmap_h, uint32_t t_grp,
+                                                    int m0, int n_grp0, int grp, int row_in_tile,
+                                                    uint32_t stage_smem, uint8_t* stage_ptr, bool elected) {
+  if (n_grp0 >= ep.N) return;  // uniform over the group: tile tail beyond N
+  uint8_t* my_row = stage_ptr + row_in_tile * 128;
+  const int sw = row_in_tile & 7;
+  if (elected) bulk_wait_read_all();   // the previous store has read the buffer
+  named_bar_sync(1 + grp, 128);
+#pragma unroll 1
+  for (int c = 0; c < 2; ++c) {
+    uint32_t rg[32], ru[32];
+    tmem_ld_32x32(t_grp + c * 32, rg);
+    tmem_ld_32x32(t_grp + 64 + c * 32, ru);
+    tmem_wait_ld();
+    const int n0 = n_grp0 + c * 32;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {   // 8 outputs = one 16-byte chunk
+      uint32_t w[4];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int i = k * 8 + h * 4;
+        float4 g = make_float4(__uint_as_float(rg[i]), __uint_as_float(rg[i + 1]), __uint_as_float(rg[i + 2]),
+                               __uint_as_float(rg[i + 3]));
+        float4 u = make_float4(__uint_as_float(ru[i]), __uint_as_float(ru[i + 1]), __uint_as_float(ru[i + 2]),
+                               __uint_as_float(ru[i + 3]));
+        if (ep.bias) {
+          const float4 bg = __ldg(reinterpret_cast<const float4*>(ep.bias + n0 + i));
+          const float4 bu = __ldg(reinterpret_cast<const float4*>(ep.bias + n0 + i + 64));
+          g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w;
+          u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
+        }
+        w[2 * h] = pack2_act(silu_f(g.x) * u.x, silu_f(g.y) * u.y, ep.act_f16);
+        w[2 * h + 1] = pack2_act(silu_f(g.z) * u.z, silu_f(g.w) * u.w, ep.act_f16);
+      }
+      *reinterpret_cast<uint4*>(my_row + (((c * 4 + k) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  fence_proxy_async_smem();
+  named_bar_sync(1 + grp, 128);
+  if (elected && m0 < ep.M) {
+    tma_store_2d(tmap_h, stage_smem, (n_grp0 >> 7) * 64, m0);
+    bulk_commit_group();
   }
 }
 
@@ -188,7 +242,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (MODE == EPI_RESID) tma_prefetch_desc(&tmap_x);
+    if (epi_staged<BN, MODE>()) tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
@@ -276,7 +330,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       bool ok = mbar_wait_bounded(bar_acc_full + 8 * acc, (it >> 1) & 1);
       if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
       // the four warps of a group share named barriers below, so they must leave together
-      if constexpr (MODE == EPI_RESID) ok = !named_bar_or(1 + col_half, 128, !ok);
+      if constexpr (epi_staged<BN, MODE>()) ok = !named_bar_or(1 + col_half, 128, !ok);
       else ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -285,13 +339,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         epilogue_resid_tma<BN>(ep, &tmap_x, t_row, m_blk * TC_BM, n_blk * BN, col_half, row_in_tile,
                                base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
                                base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      else if constexpr (MODE == EPI_SWIGLU && BN == 256)
+        epilogue_swiglu_tma(ep, &tmap_x, t_row + col_half * 128, m_blk * TC_BM, n_blk * BN + col_half * 128, col_half,
+                            row_in_tile, base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
+                            base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
       else
         epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained: hand it back to the MMA warp
       tc_fence_before();
       mbar_arrive(bar_acc_empty + 8 * acc);
     }
-    if (MODE == EPI_RESID && quarter == 0 && lane == 0) bulk_wait_all();  // reduces done before the CTA exits
+    if (epi_staged<BN, MODE>() && quarter == 0 && lane == 0) bulk_wait_all();  // bulk writes done before the CTA exits
   }
   tc_fence_before();
   __syncthreads();
@@ -360,7 +418,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (MODE == EPI_RESID) tma_prefetch_desc(&tmap_x);
+    if (epi_staged<256, MODE>()) tma_prefetch_desc(&tmap_x);
   }
   if (warp == 1) {
     tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
@@ -445,7 +503,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const bool row_ok = m < ep.M;
       bool ok = mbar_wait_bounded(bar_acc_full + 8 * acc, (it >> 1) & 1);
       if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-      if constexpr (MODE == EPI_RESID) ok = !named_bar_or(1 + col_half, 128, !ok);
+      if constexpr (epi_staged<256, MODE>()) ok = !named_bar_or(1 + col_half, 128, !ok);
       else ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -454,6 +512,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         epilogue_resid_tma<BN>(ep, &tmap_x, t_row, m_blk * 256 + (int)rank * 128, n_blk * BN, col_half, row_in_tile,
                                base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
                                base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      else if constexpr (MODE == EPI_SWIGLU)
+        epilogue_swiglu_tma(ep, &tmap_x, t_row + col_half * 128, m_blk * 256 + (int)rank * 128,
+                            n_blk * BN + col_half * 128, col_half, row_in_tile,
+                            base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
+                            base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
       else
         epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained by this warp: tell the leader's MMA thread
@@ -461,7 +524,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       __syncwarp();
       if (lane == 0) mbar_arrive_cta0(bar_acc_empty + 8 * acc);
     }
-    if (MODE == EPI_RESID && quarter == 0 && lane == 0) bulk_wait_all();
+    if (epi_staged<256, MODE>() && quarter == 0 && lane == 0) bulk_wait_all();
   }
   tc_fence_before();
   __syncthreads();
@@ -702,6 +765,10 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
     CUtensorMap tx = ta;  // only the residual epilogue reads it
     if (MODE == EPI_RESID) {
       r = make_tmap_resid_f32(&tx, ep.x, (uint64_t)M, (uint64_t)N);
+      if (r) return 1000 + r;
+    } else if (MODE == EPI_SWIGLU && (pair || wide)) {
+      // h16 [M][N / 2], 128 x 64 boxes (one accumulator group's outputs)
+      r = arcb_make_tmap_2d_16b(&tx, ep.out16, (uint64_t)M, (uint64_t)(N / 2), 128, 64, act_f16);
       if (r) return 1000 + r;
     }
     if (pair) launch_tc2<MODE>(ta, tb, tx, ep, K, act_f16, stream);
