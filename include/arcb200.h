@@ -180,6 +180,9 @@ typedef struct arcb_prefill_args {
   const int32_t* d_qblock_kv0;  /* [n_qblocks] first scratch row of the block's sequence */
   const int32_t* d_kv_row;      /* [n_tokens] scratch row of the token's K/V, < 0: none  */
   int32_t n_kv_rows;            /* scratch rows written by this call (all in [0, n_kv_rows)) */
+  int32_t kv_row_identity;      /* 1 = promise that d_kv_row[i] == i for i < n_kv_rows and < 0 after
+                                   (packed prompts with query-only rows, if any, at the end): the
+                                   scratch rows are then written with bulk tensor stores */
   float* d_logits_all;         /* optional [n_tokens][14]                      */
   int32_t n_first;
   const int32_t* d_first_row;  /* [n_first] packed row whose hidden state is read */

@@ -64,6 +64,7 @@ class PrefillArgs(C.Structure):
         ("d_kv_slot", C.c_void_p), ("d_kv_count", C.c_void_p), ("d_example_ids", C.c_void_p),
         ("n_qblocks", C.c_int32), ("d_qblock_row0", C.c_void_p), ("d_qblock_rows", C.c_void_p),
         ("d_qblock_kv0", C.c_void_p), ("d_kv_row", C.c_void_p), ("n_kv_rows", C.c_int32),
+        ("kv_row_identity", C.c_int32),
         ("d_logits_all", C.c_void_p),
         ("n_first", C.c_int32), ("d_first_row", C.c_void_p), ("d_first_seq", C.c_void_p),
         ("d_prompt_len", C.c_void_p), ("d_grid_x", C.c_void_p), ("d_grid_y", C.c_void_p),

@@ -394,7 +394,10 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
   ep.rope = e->rope; ep.max_x = c.max_x; ep.max_y = c.max_y; ep.max_z = c.max_z;
   const bool want_flash = prefill && c.attn_path == ARCB_ATTN_AUTO && pa && pa->n_qblocks > 0 && pa->d_kv_row &&
                           pa->d_qblock_kv0 && pa->n_kv_rows > 0 && arcb_attn_prefill_available();
-  if (want_flash) { ep.k16 = s->k16; ep.v16 = s->v16; ep.kv_row = pa->d_kv_row; }
+  if (want_flash) {
+    ep.k16 = s->k16; ep.v16 = s->v16; ep.kv_row = pa->d_kv_row;
+    ep.kv16_rows = pa->n_kv_rows; ep.kv16_identity = pa->kv_row_identity == 1;
+  }
   CKL(arcb_launch_gemm(s->xn16, L.w_qkv, ep, d, f16, use_tc_for(e, rows, 3 * d, d), stream), "qkv gemm");
 
   // attention

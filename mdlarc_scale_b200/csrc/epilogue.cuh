@@ -28,6 +28,8 @@ struct GemmEpilogue {
   void* k16;              // optional [n_kv_rows][d]: K of this call in the activation format
   void* v16;              //   (operands of the tensor-core prefill attention)
   const int* kv_row;      // [M] row of k16/v16 for this token, < 0: none
+  int kv16_rows;          // rows of k16 / v16
+  int kv16_identity;      // kv_row[m] == m for m < kv16_rows and < 0 after: rows can be stored as boxes
   int t_max, n_heads, d_model, n_seqs;
   const float* rope;  // cos_x | sin_x | cos_y | sin_y | cos_z | sin_z
   int max_x, max_y, max_z;

@@ -38,11 +38,13 @@ struct TcCfg {
 constexpr int EPI_STAGE_GROUP_BYTES = 128 * 32 * 4;
 template <int MODE>
 __host__ __device__ constexpr int epi_stage_bytes() {
-  return (MODE == EPI_RESID || MODE == EPI_SWIGLU) ? 2 * EPI_STAGE_GROUP_BYTES : 0;
+  return (MODE == EPI_RESID || MODE == EPI_SWIGLU || MODE == EPI_QKV_ROPE) ? 2 * EPI_STAGE_GROUP_BYTES : 0;
 }
 // epilogues that go through the staging buffers and the third tensor map
 template <int BN, int MODE>
-__host__ __device__ constexpr bool epi_staged() { return MODE == EPI_RESID || (MODE == EPI_SWIGLU && BN == 256); }
+__host__ __device__ constexpr bool epi_staged() {
+  return MODE == EPI_RESID || ((MODE == EPI_SWIGLU || MODE == EPI_QKV_ROPE) && BN == 256);
+}
 
 // Residual epilogue: x[m][n] += acc[m][n] (+ bias[n]) for this CTA's 128 rows and this group's
 // column half, 32 columns at a time.  Each thread drops its row's 32 values into the staging
@@ -138,6 +140,78 @@ __device__ __forceinline__ void epilogue_swiglu_tma(const GemmEpilogue& ep, cons
   }
 }
 
+// QKV epilogue of one 128-column accumulator group (two heads of one of the q / k / v sections; a
+// 256-column tile never straddles sections because d_model is a multiple of 256 wherever this
+// kernel is chosen).  Per head: 3D RoPE on q and k, the bf16 cache row written directly (its
+// address is per token), and the 16-bit copy -- q16, or the call's K / V scratch when its rows are
+// the packed rows themselves (kv16_identity) -- staged as a 128 x 64 box and written by one bulk
+// tensor store, which also clips the rows beyond the tensor (M, or the scratch's row count).
+__device__ __forceinline__ void epilogue_qkv_tma(const GemmEpilogue& ep, const RopeRow& rr, const CUtensorMap* tmap_q,
+                                                 const CUtensorMap* tmap_k, const CUtensorMap* tmap_v, uint32_t t_grp,
+                                                 int m0, bool row_ok, int n_grp0, int grp, int row_in_tile,
+                                                 uint32_t stage_smem, uint8_t* stage_ptr, bool elected) {
+  uint8_t* my_row = stage_ptr + row_in_tile * 128;
+  const int sw = row_in_tile & 7;
+  const int d = ep.d_model;
+#pragma unroll 1
+  for (int hh = 0; hh < 2; ++hh) {
+    const int n_head0 = n_grp0 + hh * 64;
+    if (n_head0 >= ep.N) break;  // uniform over the group
+    const int sec = n_head0 / d;            // 0 q, 1 k, 2 v
+    const int c = n_head0 - sec * d;        // column inside the section
+    const int h = c >> 6;
+    const bool staged = sec == 0 || (ep.k16 != nullptr && ep.kv16_identity);
+    if (staged) {
+      if (elected) bulk_wait_read_all();    // the previous store has read the buffer
+      named_bar_sync(1 + grp, 128);
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      uint32_t acc[32];
+      tmem_ld_32x32(t_grp + hh * 64 + half * 32, acc);
+      tmem_wait_ld();
+      float v[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(acc[i]);
+      if (sec < 2) {
+        if (half == 0) rope_rotate32<0>(ep, rr, v);
+        else rope_rotate32<16>(ep, rr, v);
+      }
+      if (sec > 0 && row_ok && rr.kv_row >= 0) {
+        __nv_bfloat16* base = (sec == 1) ? ep.kcache : ep.vcache;
+        uint4* dst = reinterpret_cast<uint4*>(base + (rr.kv_row + (long long)h * ep.t_max) * ARCB_HEAD_DIM + half * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_uint4(pack2_bf16(v[8 * q], v[8 * q + 1]), pack2_bf16(v[8 * q + 2], v[8 * q + 3]),
+                              pack2_bf16(v[8 * q + 4], v[8 * q + 5]), pack2_bf16(v[8 * q + 6], v[8 * q + 7]));
+      }
+      if (staged) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(my_row + (((half * 4 + q) ^ sw) << 4)) =
+              make_uint4(pack2_act(v[8 * q], v[8 * q + 1], ep.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], ep.act_f16),
+                         pack2_act(v[8 * q + 4], v[8 * q + 5], ep.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], ep.act_f16));
+      } else if (sec > 0 && row_ok && rr.row16 >= 0) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>((sec == 1) ? ep.k16 : ep.v16) +
+                                              (size_t)rr.row16 * d + c + half * 32);
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          dst[q] = make_uint4(pack2_act(v[8 * q], v[8 * q + 1], ep.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], ep.act_f16),
+                              pack2_act(v[8 * q + 4], v[8 * q + 5], ep.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], ep.act_f16));
+      }
+    }
+    if (staged) {
+      fence_proxy_async_smem();
+      named_bar_sync(1 + grp, 128);
+      const int limit = (sec == 0) ? ep.M : ep.kv16_rows;
+      if (elected && m0 < limit) {
+        tma_store_2d(sec == 0 ? tmap_q : (sec == 1 ? tmap_k : tmap_v), stage_smem, c, m0);
+        bulk_commit_group();
+      }
+    }
+  }
+}
+
 // Drains one accumulator tile (this thread's row, the 32-column chunks of its column half) from
 // TMEM through the epilogue MODE.  t_row: TMEM address of the row's first accumulator column;
 // n_tile0: first output column of the tile.  tcgen05.ld is warp-collective, so every lane runs the
@@ -209,7 +283,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmEpilogue& ep, uint32_t t
 template <int BN, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_x, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
+               const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
+               const __grid_constant__ CUtensorMap tmap_z, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
                int tiles_total) {
   using Cfg = TcCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
@@ -343,6 +418,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         epilogue_swiglu_tma(ep, &tmap_x, t_row + col_half * 128, m_blk * TC_BM, n_blk * BN + col_half * 128, col_half,
                             row_in_tile, base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
                             base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      else if constexpr (MODE == EPI_QKV_ROPE && BN == 256) {
+        RopeRow rr;
+        rr.x = rr.y = rr.z = 0; rr.kv_row = -1; rr.row16 = -1;
+        if (row_ok) rr = rope_row_ctx(ep, m);
+        epilogue_qkv_tma(ep, rr, &tmap_x, &tmap_y, &tmap_z, t_row + col_half * 128, m_blk * TC_BM, row_ok,
+                         n_blk * BN + col_half * 128, col_half, row_in_tile,
+                         base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
+                         base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      }
       else
         epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained: hand it back to the MMA warp
@@ -383,7 +467,8 @@ struct Tc2Cfg {
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const __grid_constant__ CUtensorMap tmap_x, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
+                const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
+                const __grid_constant__ CUtensorMap tmap_z, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
                 int tiles_total) {
   using Cfg = Tc2Cfg;
   constexpr int BN = Cfg::BN;
@@ -517,6 +602,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                             n_blk * BN + col_half * 128, col_half, row_in_tile,
                             base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
                             base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      else if constexpr (MODE == EPI_QKV_ROPE) {
+        RopeRow rr;
+        rr.x = rr.y = rr.z = 0; rr.kv_row = -1; rr.row16 = -1;
+        if (row_ok) rr = rope_row_ctx(ep, m);
+        epilogue_qkv_tma(ep, rr, &tmap_x, &tmap_y, &tmap_z, t_row + col_half * 128, m_blk * 256 + (int)rank * 128,
+                         row_ok, n_blk * BN + col_half * 128, col_half, row_in_tile,
+                         base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
+                         base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+      }
       else
         epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
       // accumulator drained by this warp: tell the leader's MMA thread
@@ -722,25 +816,25 @@ int arcb_gemm_init() {
 }
 
 template <int BN, int MODE>
-static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const GemmEpilogue& ep,
-                      int K, int act_f16, cudaStream_t stream) {
+static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
+                      const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + BN - 1) / BN, tiles_m = (ep.M + TC_BM - 1) / TC_BM;
   const int tiles = tiles_n * tiles_m;
   const int sms = g_num_sms > 0 ? g_num_sms : 148;
   const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
   gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, TC_THREADS, TcCfg<BN>::SMEM_BYTES + epi_stage_bytes<MODE>(),
-                             stream>>>(ta, tb, tx, ep, K, idesc, tiles_n, tiles);
+                             stream>>>(ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
 }
 
 template <int MODE>
-static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const GemmEpilogue& ep,
-                       int K, int act_f16, cudaStream_t stream) {
+static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
+                       const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + 255) / 256, tiles_m = (ep.M + 255) / 256;
   const int tiles = tiles_n * tiles_m;
   const int pairs = tiles < g_max_pairs ? tiles : g_max_pairs;
   const uint32_t idesc = umma_idesc_f16(256, 256, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
   gemm_tc2_kernel<MODE><<<2 * pairs, TC_THREADS, Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>(), stream>>>(
-      ta, tb, tx, ep, K, idesc, tiles_n, tiles);
+      ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
 }
 
 int arcb_gemm_max_pairs() { return g_max_pairs; }
@@ -753,10 +847,13 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
     // 128 x 256 tiles (one CTA per SM, persistent) unless that leaves most SMs without a tile
     const int sms = g_num_sms > 0 ? g_num_sms : 148;
     const int tiles256 = ((N + 255) / 256) * ((M + TC_BM - 1) / TC_BM);
-    const bool wide = tiles256 * 10 >= sms * 7;
+    // the QKV epilogue of the 256-column kernels needs tiles that stay inside one of the q / k / v sections
+    const bool allow256 = !(MODE == EPI_QKV_ROPE && ep.d_model % 256 != 0);
+    const bool wide = allow256 && tiles256 * 10 >= sms * 7;
     // 256 x 256 tiles on CTA pairs when there are enough of them to occupy the machine
     const int tiles2 = ((N + 255) / 256) * ((M + 255) / 256);
-    const bool pair = g_max_pairs > 0 && (tc_variant == 2 || (tc_variant == 0 && tiles2 * 10 >= g_max_pairs * 7));
+    const bool pair = allow256 && g_max_pairs > 0 &&
+                      (tc_variant == 2 || (tc_variant == 0 && tiles2 * 10 >= g_max_pairs * 7));
     CUtensorMap ta, tb;
     int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
     if (r) return 1000 + r;
@@ -771,9 +868,21 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
       r = arcb_make_tmap_2d_16b(&tx, ep.out16, (uint64_t)M, (uint64_t)(N / 2), 128, 64, act_f16);
       if (r) return 1000 + r;
     }
-    if (pair) launch_tc2<MODE>(ta, tb, tx, ep, K, act_f16, stream);
-    else if (wide) launch_tc<256, MODE>(ta, tb, tx, ep, K, act_f16, stream);
-    else launch_tc<128, MODE>(ta, tb, tx, ep, K, act_f16, stream);
+    CUtensorMap ty = ta, tz = ta;
+    if (MODE == EPI_QKV_ROPE && (pair || wide)) {
+      // q16 [M][d] and, when its rows are the packed rows, the K / V scratch [kv16_rows][d]: 128 x 64 boxes
+      r = arcb_make_tmap_2d_16b(&tx, ep.out16, (uint64_t)M, (uint64_t)ep.d_model, 128, 64, act_f16);
+      if (r) return 1000 + r;
+      if (ep.k16 && ep.kv16_identity && ep.kv16_rows > 0) {
+        r = arcb_make_tmap_2d_16b(&ty, ep.k16, (uint64_t)ep.kv16_rows, (uint64_t)ep.d_model, 128, 64, act_f16);
+        if (r) return 1000 + r;
+        r = arcb_make_tmap_2d_16b(&tz, ep.v16, (uint64_t)ep.kv16_rows, (uint64_t)ep.d_model, 128, 64, act_f16);
+        if (r) return 1000 + r;
+      }
+    }
+    if (pair) launch_tc2<MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
+    else if (wide) launch_tc<256, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
+    else launch_tc<128, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
   } else {
     dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
     gemm_simt_kernel<MODE><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a16),

@@ -254,6 +254,7 @@ class Session:
             d_example_ids=_ptr(example_ids),
             n_qblocks=plan.n_qblocks, d_qblock_row0=_ptr(plan.qblock_row0), d_qblock_rows=_ptr(plan.qblock_rows),
             d_qblock_kv0=_ptr(plan.qblock_kv0), d_kv_row=_ptr(plan.kv_row), n_kv_rows=plan.n_kv_rows,
+            kv_row_identity=int(bool(plan.kv_row_identity)),
             d_logits_all=_ptr(logits_all),
             n_first=plan.n_first, d_first_row=_ptr(plan.first_row), d_first_seq=_ptr(plan.first_seq),
             d_prompt_len=_ptr(plan.prompt_len), d_grid_x=_ptr(plan.grid_x), d_grid_y=_ptr(plan.grid_y),
@@ -304,6 +305,7 @@ class PrefillPlan:
     grid_x: torch.Tensor | None = None
     grid_y: torch.Tensor | None = None
     grid_in_output: torch.Tensor | None = None
+    kv_row_identity: bool = False   # kv_row[i] == i for i < n_kv_rows and < 0 after
 
     def to(self, device) -> "PrefillPlan":
         def mv(t):
@@ -312,7 +314,7 @@ class PrefillPlan:
                            mv(self.kv_count), self.n_qblocks, mv(self.qblock_row0), mv(self.qblock_rows),
                            mv(self.qblock_kv0), mv(self.kv_row), self.n_kv_rows,
                            self.n_first, mv(self.first_row), mv(self.first_seq), mv(self.prompt_len),
-                           mv(self.grid_x), mv(self.grid_y), mv(self.grid_in_output))
+                           mv(self.grid_x), mv(self.grid_y), mv(self.grid_in_output), self.kv_row_identity)
 
     def h2d_bytes(self) -> int:
         n = 0
@@ -429,12 +431,14 @@ def plan_prefill(ids: np.ndarray, pos: np.ndarray, mask: np.ndarray, rows: np.nd
     local = np.searchsorted(rows, seq)  # index of each token's sequence within this call (rows is sorted)
     kv_row = np.where(slot >= 0, kv_base[local] + slot, -1).astype(np.int32)
     qb_kv0 = kv_base[local[qb0]].astype(np.int32) if len(qb0) else np.zeros(0, np.int32)
+    n_kv = int(lens.sum())
+    identity = bool(np.array_equal(kv_row[:n_kv], np.arange(n_kv, dtype=np.int32)) and (kv_row[n_kv:] < 0).all())
     return PrefillPlan(
         n_tokens=len(tok), token_ids=torch.from_numpy(tok), pos_xyz=torch.from_numpy(np.ascontiguousarray(pxyz)),
         seq=torch.from_numpy(seq), kv_slot=torch.from_numpy(slot), kv_count=torch.from_numpy(cnt),
         n_qblocks=len(qb0), qblock_row0=torch.from_numpy(qb0), qblock_rows=torch.from_numpy(qbn),
         qblock_kv0=torch.from_numpy(qb_kv0), kv_row=torch.from_numpy(kv_row), n_kv_rows=int(lens.sum()),
-        n_first=n_first, **plan_first)
+        n_first=n_first, kv_row_identity=identity, **plan_first)
 
 
 def chunk_rows(lens: np.ndarray, max_tokens: int) -> list[np.ndarray]:

@@ -164,7 +164,7 @@ class TaskTable:
             kv_row=out[7, :total], n_kv_rows=total,
             n_first=n, first_row=up(tok_off[1:] - 1), first_seq=d_rows, prompt_len=up(lens),
             # every prompt ends with IO_SEP: next cell is (0, 0) of the output (src/inference.py:171-221)
-            grid_x=up(zeros), grid_y=up(zeros), grid_in_output=up(zeros + 1))
+            grid_x=up(zeros), grid_y=up(zeros), grid_in_output=up(zeros + 1), kv_row_identity=True)
         plan._status = status          # read by check_status after the stream has run
         plan._keep = (d_tpl, d_dih, d_perm, d_off, out)
         return plan
