@@ -238,6 +238,19 @@ def test_small_model_many_tokens_wide_gemm_tiles():
     err = (got[mask_t] - want[mask_t]).abs().max().item()
     print(f"small model, {int(mask.sum())} tokens: max abs logit error {err:.4f}")
     assert err < TOL
+    # The generation path packs the same prompts without padded rows, so its K / V scratch rows are
+    # the packed rows themselves and leave the QKV epilogue as bulk tensor stores (the padded forward
+    # above writes them row by row): the first-token logits must agree with the forward's logits at
+    # each prompt's last position.
+    from mdlarc_scale_b200.inference import generate_tokens
+    tr = generate_tokens(eng, ids, pos, mask, ex.numpy(), 2, stop_on_end=False, want_logits=True)
+    last = mask.sum(axis=1) - 1
+    rows = torch.arange(len(prompts))
+    first = tr.first_logits.cpu()
+    d_paths = (first - got[rows, torch.from_numpy(last)]).abs().max().item()
+    d_oracle = (first - want[rows, torch.from_numpy(last)]).abs().max().item()
+    print(f"first-token logits: packed vs padded plan {d_paths:.2e}, vs oracle {d_oracle:.4f}")
+    assert d_paths < 1e-3 and d_oracle < TOL
     eng.close()
 
 
