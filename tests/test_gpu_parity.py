@@ -254,6 +254,46 @@ def test_small_model_many_tokens_wide_gemm_tiles():
     eng.close()
 
 
+def test_full_size_decode_workload_properties():
+    """The benchmark workload at its full size (large model, 1024 sequences, 931 generated tokens
+    each, END suppressed, a 94 GB cache), where the CPU oracle cannot follow: properties that do not
+    depend on size.  Two runs give bitwise identical tokens; every token is in the vocabulary; and rows
+    generated again in a batch of 8 (other GEMM kernels, split-K attention) give the same tokens up to
+    the first step whose own top-2 logit margin is below the tolerance."""
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+    from gpu_util import tokens_agree
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    cfg, sd = synthetic.seeded_weights("large", 0, 8.0)
+    eng = Engine(sd, cfg, "cuda:0")
+    n, max_new = 1024, 931
+    tasks = synthetic.capped_tasks(0, n, 2, 2, 3, 10, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    runs = []
+    for _ in range(2):
+        tr = generate_tokens(eng, ids, pos, mask, None, max_new, stop_on_end=False)
+        runs.append(tr.tokens.cpu().numpy().copy())
+        del tr
+    assert runs[0].shape == (n, max_new)
+    assert np.array_equal(runs[0], runs[1])
+    assert runs[0].min() >= 0 and runs[0].max() <= 13
+    assert len(np.unique(runs[0])) > 3                      # not a degenerate constant stream
+    sel = np.array([0, 5, 6, 17, 300, 511, 777, 1023])
+    small = generate_tokens(eng, ids[sel], pos[sel], mask[sel], None, max_new, stop_on_end=False, want_logits=True)
+    small_tok = small.tokens.cpu().numpy()
+    small_logits = small.step_logits.cpu().numpy()
+    agree_len = []
+    for k, row in enumerate(sel.tolist()):
+        ok, where = tokens_agree(runs[0][row].tolist(), small_tok[k].tolist(), list(small_logits[k]), TOL)
+        assert ok, (row, where)
+        agree_len.append(max_new if where < 0 else where)
+    print(f"full-size workload: identical prefix lengths vs batch-of-8 runs {agree_len}")
+    eng.close()
+
+
 @pytest.mark.parametrize("name", ["plain", "varied"])
 def test_constrained_generation_vs_reference(engines, golden_model, name):
     """Soft-constrained decoding (palette, target shape, disallowed tokens) inside the token-picking
