@@ -257,6 +257,49 @@ def profile_prefill(args):
                       "tflops": (lin + att) / t / 1e12, "frac_of_bf16_burst_peak": (lin + att) / t / 1e12 / 1672.1}))
 
 
+def profile_long_context(args):
+    """One wave of the prefill-heavy large configuration end to end: `--profile-long` prompts of 5
+    pairs of 30x30 grids + a 30x30 test input (10 247 tokens each), then `--max-new` greedy tokens with
+    END suppressed.  Prints prefill and decode rates and the decode-attention bandwidth over the long
+    cache (algorithmic bytes = cached positions x 61 440 B per sequence per step)."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    dev = torch.device("cuda", 0)
+    cfg, sd = model_state()
+    cfg["max_seq_len"] = 16384
+    engine = Engine(sd, cfg, dev)
+    n = args.profile_long
+    tasks = synthetic.capped_tasks(3, n, 5, 5, 30, 30, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    lens = mask.sum(axis=1)
+    generate_tokens(engine, ids[:2], pos[:2], mask[:2], None, 4, stop_on_end=False)   # warm-up
+
+    def timed(max_new):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        e0.record()
+        tr = generate_tokens(engine, ids, pos, mask, None, max_new, stop_on_end=False)
+        e1.record()
+        e1.synchronize()
+        del tr
+        return e0.elapsed_time(e1) / 1e3
+
+    t_prefill = timed(1)
+    t_all = timed(MAX_NEW)
+    t_decode = t_all - t_prefill
+    steps = MAX_NEW - 1
+    mean_len = float(lens.mean()) + steps / 2.0
+    attn_bytes = n * mean_len * 61440.0 * steps
+    print(json.dumps({"profile": "long context", "sequences": n, "prompt_tokens": int(lens.sum()),
+                      "new_tokens": MAX_NEW, "prefill_s": t_prefill, "prefill_tokens_per_s": int(lens.sum()) / t_prefill,
+                      "decode_s": t_decode, "ms_per_decode_step": t_decode / steps * 1e3,
+                      "generated_tokens_per_s": n * MAX_NEW / t_all,
+                      "kv_bytes_read_per_step": attn_bytes / steps,
+                      "decode_step_gbs_counting_kv_only": attn_bytes / t_decode / 1e9}))
+
+
 def run_ours(args, rank, world, local_rank):
     from mdlarc_scale_b200 import _lib
     from mdlarc_scale_b200.engine import Engine, chunk_rows, plan_prefill
@@ -431,6 +474,8 @@ def main():
                     help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
     ap.add_argument("--profile-prefill", type=int, default=0, metavar="PAIRS",
                     help="only time the prefill of ~64k tokens of prompts with PAIRS 30x30 train pairs")
+    ap.add_argument("--profile-long", type=int, default=0, metavar="SEQS",
+                    help="only run one wave of SEQS 10 247-token prompts + --max-new tokens (long-context decode)")
     ap.add_argument("--max-new", type=int, default=MAX_NEW,
                     help="tokens generated per sequence (the workload uses 931; smaller only for profiling)")
     args = ap.parse_args()
@@ -448,6 +493,9 @@ def main():
         return
     if args.profile_prefill > 0:
         profile_prefill(args)
+        return
+    if args.profile_long > 0:
+        profile_long_context(args)
         return
     run_ours(args, rank, world, local_rank)
 
