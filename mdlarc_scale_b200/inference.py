@@ -333,13 +333,14 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
                                sample_temperature: float = 0.0, sample_top_k: int | None = None,
                                constrain_decoding: bool = False, palette_penalty: float = 2.0,
                                shape_penalty: float = 2.0, batched: bool = True, use_compile: bool = False,
-                               max_batch_size: int = 16):
+                               max_batch_size: int = 16, merge_chunks: bool = True):
     """Candidates under all augmentations for AAIVR voting (``src/inference.py:697-920``).
 
     Returns ``[(grid | None, dihedral_idx, colour_perm | None), ...]`` in the reference's order.
-    Chunks of ``max_batch_size`` left-padded prompts go through ``generate_output`` exactly as the
-    reference's batched path does, so each chunk reproduces its semantics (including which
-    hidden state yields the first token of a left-padded row).
+    Prompts are laid out in chunks of ``max_batch_size`` left-padded rows exactly as the reference's
+    batched path does, so each chunk reproduces its semantics (including which hidden state yields
+    the first token of a left-padded row); with ``merge_chunks`` the chunks share one session
+    (one prefill, one decode loop for all of them) instead of one ``generate_output`` call each.
     """
     device = torch.device(device)
     engine = _resolve_engine(model, device)
@@ -348,14 +349,41 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
     palettes = shapes = None
     if constrain_decoding:
         palettes, shapes = augmented_constraints(task, test_idx, info)
+    chunks = [slice(c0, min(c0 + max_batch_size, len(prompts))) for c0 in range(0, len(prompts), max_batch_size)]
+    padded = [pad_prompts(prompts[c], positions[c], left=True) for c in chunks]
+    width = max((p[0].shape[1] for p in padded), default=0)
     out = []
-    for c0 in range(0, len(prompts), max_batch_size):
-        chunk = slice(c0, min(c0 + max_batch_size, len(prompts)))
-        ids, pos, mask = pad_prompts(prompts[chunk], positions[chunk], left=True)
+    if merge_chunks and len(chunks) > 1 and width + max_output_tokens <= engine.max_seq_len:
+        # All chunks in ONE session.  Each chunk keeps its own left-padded layout (what decides which
+        # hidden state yields a row's first token, src/inference.py:420-423); the narrower chunks
+        # get masked columns on the right, which changes neither a row's valid keys nor the padded
+        # index len - 1.  No chunk is clamped by max_seq_len here, so every row may generate
+        # max_output_tokens as it would in its own chunk.
+        n = len(prompts)
+        ids = np.full((n, width), END_TOKEN_ID, dtype=np.int64)
+        pos = np.zeros((n, width, 3), dtype=np.int64)
+        mask = np.zeros((n, width), dtype=bool)
+        for c, (ci, cp, cm) in zip(chunks, padded):
+            w = ci.shape[1]
+            ids[c, :w], pos[c, :w], mask[c, :w] = ci, cp, cm
+        cons = None
+        if constrain_decoding:
+            cons = _constraints_dict(chunk_constraints(palettes, shapes, palette_penalty, shape_penalty), n)
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if sample_temperature > 0 else 0
+        trace = generate_tokens(engine, ids, pos, mask, np.full(n, example_id, dtype=np.int64), max_output_tokens,
+                                stop_on_end=True, constraints=cons, temperature=float(sample_temperature),
+                                top_k=sample_top_k, sample_seed=seed)
+        gen = trace.tokens.cpu().tolist()
+        for i, (d_idx, tag) in enumerate(info):
+            # the reference reads the grid after the last IO_SEP of padding + prompt + generated
+            # tokens (src/inference.py:906-915); the padding (END tokens before the prompt) plays no part
+            out.append((_grid_after_last_sep([int(t) for t in prompts[i]] + gen[i]), d_idx, tag))
+        return out
+    for c, (ids, pos, mask) in zip(chunks, padded):
         ids_t = torch.from_numpy(ids).to(device)
         cons = None
         if constrain_decoding:
-            cons = chunk_constraints(palettes[chunk], shapes[chunk], palette_penalty, shape_penalty)
+            cons = chunk_constraints(palettes[c], shapes[c], palette_penalty, shape_penalty)
         full = generate_output(engine, ids_t, torch.from_numpy(pos).to(device),
                                torch.full((ids.shape[0],), example_id, dtype=torch.long, device=device),
                                attention_mask=torch.from_numpy(mask).to(device),
@@ -363,6 +391,6 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
                                top_k=sample_top_k, stop_on_end=True, constraints=cons)
         rows = full.cpu().tolist()
         for i, toks in enumerate(rows):
-            d_idx, tag = info[c0 + i]
+            d_idx, tag = info[c.start + i]
             out.append((_grid_after_last_sep(toks), d_idx, tag))
     return out

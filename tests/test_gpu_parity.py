@@ -146,6 +146,13 @@ def test_predict_with_augmentations_and_vote(engines):
     mine = aaivr_predict(preds, 2, task["test"][0]["input"], rng=random.Random(5))
     ref = arc_vote.aaivr_predict(preds, 2, task["test"][0]["input"], rng=random.Random(5))
     assert mine == ref  # votes bit-exact given identical candidates
+    # all chunks in one session vs one generate_output call per chunk of 16: same candidates (another
+    # batch shape may flip a near-tie token, so most, not all, must be identical)
+    per_chunk = predict_with_augmentations(eng, task, 0, "cuda:0", num_color_perms=3, max_output_tokens=24,
+                                           merge_chunks=False)
+    assert [(d, p) for _, d, p in per_chunk] == [(d, p) for _, d, p in preds]
+    same = sum(a[0] == b[0] for a, b in zip(preds, per_chunk))
+    assert same >= 20, same
     # constrained decoding through the same entry point (palette + shape from the train pairs)
     cpreds = predict_with_augmentations(eng, task, 0, "cuda:0", num_color_perms=3, max_output_tokens=24,
                                         constrain_decoding=True, palette_penalty=2.0, shape_penalty=2.0)
