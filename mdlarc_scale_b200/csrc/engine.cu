@@ -3,6 +3,7 @@
 #include <atomic>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -578,11 +579,28 @@ extern "C" int arcb_op_rmsnorm(const float* x, const float* w, void* out16, int3
   return ARCB_OK;
 }
 
+// The shared-memory opt-in of the GEMM kernels is a per-device attribute: do it once for every
+// device a standalone operator is called on (engines do it when they are created).
+static int ensure_gemm_init() {
+  static std::mutex mu;
+  static bool done[64] = {false};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return arcb_gemm_init();
+  std::lock_guard<std::mutex> lock(mu);
+  if (!done[dev]) {
+    const int r = arcb_gemm_init();
+    if (r) return r;
+    done[dev] = true;
+  }
+  return 0;
+}
+
 extern "C" int arcb_op_gemm(const void* a16, const void* w, float* y, int32_t M, int32_t N, int32_t K,
                             int32_t act_format, int32_t gemm_path, void* stream) {
   if (!a16 || !w || !y || M <= 0) return fail(ARCB_E_ARG, "bad gemm arguments");
-  static bool inited = false;
-  if (!inited) { CKL(arcb_gemm_init(), "gemm init"); inited = true; }
+  CKL(ensure_gemm_init(), "gemm init");
   if (N % 128 || K % 32) return fail(ARCB_E_ARG, "gemm needs N % 128 == 0 and K % 32 == 0");
   const int variant = gemm_path == ARCB_GEMM_TC_1CTA ? 1 : (gemm_path == ARCB_GEMM_TC_2CTA ? 2 : 0);
   bool tc = gemm_path == ARCB_GEMM_TC || variant != 0 || (gemm_path == ARCB_GEMM_AUTO && M > 32);
@@ -599,8 +617,7 @@ extern "C" int arcb_op_gemm(const void* a16, const void* w, float* y, int32_t M,
 extern "C" int arcb_op_gemm_residual(const void* a16, const void* w, const float* bias, float* x, int32_t M,
                                      int32_t N, int32_t K, int32_t act_format, int32_t gemm_path, void* stream) {
   if (!a16 || !w || !x || M <= 0) return fail(ARCB_E_ARG, "bad gemm arguments");
-  static bool inited = false;
-  if (!inited) { CKL(arcb_gemm_init(), "gemm init"); inited = true; }
+  CKL(ensure_gemm_init(), "gemm init");
   if (N % 128 || K % 32) return fail(ARCB_E_ARG, "gemm needs N % 128 == 0 and K % 32 == 0");
   const int variant = gemm_path == ARCB_GEMM_TC_1CTA ? 1 : (gemm_path == ARCB_GEMM_TC_2CTA ? 2 : 0);
   bool tc = gemm_path == ARCB_GEMM_TC || variant != 0 || (gemm_path == ARCB_GEMM_AUTO && M > 32);
