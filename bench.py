@@ -466,8 +466,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=1024, help="sequences per GPU per step")
-    ap.add_argument("--cpu-seqs", type=int, default=16)
-    ap.add_argument("--cpu-steps", type=int, default=48)
+    ap.add_argument("--cpu-seqs", type=int, default=32)
+    ap.add_argument("--cpu-steps", type=int, default=112)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
     ap.add_argument("--profile-attn", type=int, default=0, metavar="T",
