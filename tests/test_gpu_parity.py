@@ -301,6 +301,43 @@ def test_full_size_decode_workload_properties():
     eng.close()
 
 
+def test_medium_model_logits_within_tolerance():
+    """The voting configuration's model (medium: d 1024, 16 heads, 8 layers, d_ff 2752) on ~2500
+    packed prompt tokens: CTA-pair GEMMs with a half-filled last SwiGLU tile (5504 = 21.5 x 256
+    columns), flash prefill, and 8 teacher-forced decode steps, against the fp32 oracle."""
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    from mdlarc_scale_b200.transformer import forward_logits
+    cfg = om.make_config("medium", max_seq_len=4096)
+    sd = om.round_bf16(om.perturb_state(om.init_state(cfg, seed=5), seed=6))
+    eng = Engine(sd, cfg, "cuda:0")
+    tasks = synthetic.capped_tasks(81, 4, 2, 3, 8, 14, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    assert sum(len(p) for p in prompts) > 2000
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
+    ex = torch.arange(len(prompts)) + 3
+    got = forward_logits(eng, ids_t, pos_t, ex, mask_t).cpu()
+    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
+    err = (got[mask_t] - want[mask_t]).abs().max().item()
+    n_new = 8
+    forced = np.random.default_rng(1).integers(0, 10, size=(len(prompts), n_new)).astype(np.int32)
+    forced[:, 3] = 11
+    tr = generate_tokens(eng, ids, pos, mask, ex.numpy(), n_new, stop_on_end=False, forced=forced, want_logits=True)
+    worst = 0.0
+    for b, p in enumerate(prompts):
+        full = list(p) + forced[b].tolist()
+        fpos = torch.from_numpy(ot.positions_3d(full))[None]
+        ref = om.forward(sd, cfg, torch.tensor([full]), fpos, ex[b:b + 1])[0]
+        worst = max(worst, (tr.step_logits[b].cpu() - ref[len(p) - 1: len(p) - 1 + n_new]).abs().max().item())
+    print(f"medium model, {int(mask.sum())} tokens: prompt logits {err:.4f}, decode-step logits {worst:.4f}")
+    assert err < TOL and worst < TOL
+    eng.close()
+
+
 @pytest.mark.parametrize("name", ["plain", "varied"])
 def test_constrained_generation_vs_reference(engines, golden_model, name):
     """Soft-constrained decoding (palette, target shape, disallowed tokens) inside the token-picking
