@@ -199,6 +199,25 @@ def _grid_after_last_sep(tokens: list[int]):
     return decode_output_grid(tokens[seps[-1]:]) if seps else None
 
 
+def predict_grid(model, input_grids, output_grids, test_input, device, example_id: int = 0,
+                 max_output_tokens: int = 900, temperature: float = 0.0, top_k: int | None = None,
+                 use_compile: bool = False, constraints: "DecodingConstraints | None" = None):
+    """Output grid predicted for ``test_input`` given the training pairs, or None when nothing
+    decodable follows the last IO_SEP (``src/inference.py:631-694``): one unpadded prompt through
+    ``generate_output`` with END stopping."""
+    toks: list[int] = []
+    for inp, out in zip(input_grids, output_grids, strict=True):
+        toks += encode_example(inp, out)
+    toks += encode_example(test_input, None)
+    device = torch.device(device)
+    ids = torch.tensor([toks], dtype=torch.long, device=device)
+    pos = torch.from_numpy(compute_positions_3d(toks)[None]).to(device)
+    out = generate_output(model, ids, pos, torch.tensor([example_id], dtype=torch.long, device=device),
+                          max_new_tokens=max_output_tokens, temperature=temperature, top_k=top_k,
+                          stop_on_end=True, constraints=constraints)
+    return _grid_after_last_sep(out[0].cpu().tolist())
+
+
 def build_augmented_prompts(task: dict, test_idx: int, use_train_examples: bool = True,
                             num_color_perms: int = 8, num_samples: int = 1):
     """All (dihedral x colour-permutation x sample) prompts of one test input, in the reference's
@@ -349,6 +368,38 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
     palettes = shapes = None
     if constrain_decoding:
         palettes, shapes = augmented_constraints(task, test_idx, info)
+    if not batched:
+        # The reference's sequential path runs every variant alone and unpadded
+        # (src/inference.py:923-1003).  A right-padded batch gives each row exactly that (its keys,
+        # its last token), so all variants share one session unless max_seq_len would cut some
+        # rows shorter than others, in which case they run one by one.
+        lens = [len(p) for p in prompts]
+        out = []
+        if lens and max(lens) + max_output_tokens <= engine.max_seq_len:
+            ids, pos, mask = pad_prompts(prompts, positions, left=False)
+            n = len(prompts)
+            cons = None
+            if constrain_decoding:
+                cons = _constraints_dict(chunk_constraints(palettes, shapes, palette_penalty, shape_penalty), n)
+            seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if sample_temperature > 0 else 0
+            trace = generate_tokens(engine, ids, pos, mask, np.full(n, example_id, dtype=np.int64),
+                                    max_output_tokens, stop_on_end=True, constraints=cons,
+                                    temperature=float(sample_temperature), top_k=sample_top_k, sample_seed=seed)
+            gen = trace.tokens.cpu().tolist()
+            for i, (d_idx, tag) in enumerate(info):
+                out.append((_grid_after_last_sep([int(t) for t in prompts[i]] + gen[i]), d_idx, tag))
+            return out
+        for i, (d_idx, tag) in enumerate(info):
+            cons = None
+            if constrain_decoding:
+                cons = chunk_constraints(palettes[i:i + 1], shapes[i:i + 1], palette_penalty, shape_penalty)
+            ids_t = torch.tensor([[int(t) for t in prompts[i]]], dtype=torch.long, device=device)
+            full = generate_output(engine, ids_t, torch.from_numpy(np.asarray(positions[i])[None]).to(device),
+                                   torch.tensor([example_id], dtype=torch.long, device=device),
+                                   max_new_tokens=max_output_tokens, temperature=sample_temperature,
+                                   top_k=sample_top_k, stop_on_end=True, constraints=cons)
+            out.append((_grid_after_last_sep(full[0].cpu().tolist()), d_idx, tag))
+        return out
     chunks = [slice(c0, min(c0 + max_batch_size, len(prompts))) for c0 in range(0, len(prompts), max_batch_size)]
     padded = [pad_prompts(prompts[c], positions[c], left=True) for c in chunks]
     width = max((p[0].shape[1] for p in padded), default=0)

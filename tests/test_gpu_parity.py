@@ -159,6 +159,43 @@ def test_predict_with_augmentations_and_vote(engines):
     assert len(cpreds) == 24 and sorted({d for _, d, _ in cpreds}) == list(range(8))
 
 
+def test_predict_grid_and_sequential_augmentations(engines):
+    """predict_grid (tests/test_inference.py:155-220: a grid or None, several train pairs, varying
+    sizes) against the oracle's greedy generation of the same unpadded prompt, and the sequential
+    (batched=False) augmentation path: reference order, and its identity variant is predict_grid's row."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import (_grid_after_last_sep, generate_output, predict_grid,
+                                             predict_with_augmentations)
+    eng, cfg, sd = engines["varied", "tc-flash"]
+    for seed, k, lo, hi in ((43, 1, 2, 4), (44, 3, 1, 6), (45, 2, 5, 9)):
+        task = synthetic.capped_tasks(seed, 1, k, k, lo, hi, None)[0]
+        ins = [p["input"] for p in task["train"]]
+        outs = [p["output"] for p in task["train"]]
+        test_in = task["test"][0]["input"]
+        got = predict_grid(eng, ins, outs, test_in, "cuda:0", example_id=2, max_output_tokens=40)
+        assert got is None or (isinstance(got, list) and all(isinstance(r, list) for r in got))
+        toks = []
+        for a, b in zip(ins, outs):
+            toks += ot.encode_example(a, b)
+        toks += ot.encode_example(test_in, None)
+        ids = torch.tensor([toks])
+        pos = torch.from_numpy(ot.positions_3d(toks))[None]
+        ref = om.generate(sd, cfg, ids, pos, torch.tensor([2]), None, max_new_tokens=40, stop_on_end=True,
+                          keep_logits=True)
+        mine = generate_output(eng, ids.cuda(), pos.cuda(), torch.tensor([2]).cuda(), max_new_tokens=40)[0].cpu().tolist()
+        assert got == _grid_after_last_sep(mine)
+        assert got == ot.decode_output_grid(mine[max(i for i, v in enumerate(mine) if v == 12):])
+        ok, where = tokens_agree(first_end_trim(mine[len(toks):]), first_end_trim(ref.tokens[0, len(toks):].tolist()),
+                                 [lg[0].numpy() for lg in ref.logits], TOL)
+        assert ok, (seed, where)
+    with pytest.raises(ValueError):                      # zip(strict=True) on the train pairs
+        predict_grid(eng, [[[1]]], [], [[1]], "cuda:0")
+    task = synthetic.capped_tasks(41, 1, 2, 2, 2, 5, None)[0]
+    seq = predict_with_augmentations(eng, task, 0, "cuda:0", num_color_perms=3, max_output_tokens=24, batched=False)
+    assert len(seq) == 24 and [d for _, d, _ in seq] == [d for d in range(8) for _ in range(3)]
+    assert seq[0][2] is None and seq[1][2] is not None
+
+
 def test_large_model_logits_within_tolerance():
     """The benchmark model (large: d 1280, 20 heads, 12 layers, d_ff 3392), production kernels:
     all prompt positions and 12 teacher-forced decode steps against the fp32 oracle forward on the
