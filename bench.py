@@ -300,6 +300,81 @@ def profile_long_context(args):
                       "decode_step_gbs_counting_kv_only": attn_bytes / t_decode / 1e9}))
 
 
+def profile_fanout(args):
+    """The fan-out kernels at the size of the voting configuration (400 synthetic tasks x 8 dihedral
+    x 20 colour permutations = 64 000 variants), each as ONE launch through the C ABI with its
+    index arrays already on the device: device-side prompt construction of all variants, and
+    candidate canonicalisation of 64 000 rows of 931 tokens.  Prints the algorithmic bytes (arrays
+    written / read once) and the achieved bandwidth, plus the host-side cost of `TaskTable`."""
+    import ctypes as C
+    from mdlarc_scale_b200 import _lib, fanout, synthetic
+    lib = _lib.load()
+    dev = torch.device("cuda", 0)
+    tasks = synthetic.capped_tasks(2, args.profile_fanout, 2, 4, 1, 30, 2048)
+    t0 = time.perf_counter()
+    table = fanout.TaskTable(tasks, dev, num_color_perms=20)
+    vt = table.variants()
+    t_table = time.perf_counter() - t0
+    n = len(vt)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def up(a):
+        return torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+
+    def timed(fn):
+        best = None
+        for _ in range(4):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(dev)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            best = e0.elapsed_time(e1) if best is None else min(best, e0.elapsed_time(e1))
+        return best
+
+    tok_off = np.concatenate([[0], np.cumsum(vt.length)]).astype(np.int64)
+    total = int(tok_off[-1])
+    d_tpl, d_dih, d_perm, d_off = up(vt.template), up(vt.dihedral), up(vt.perm), up(tok_off)
+    out = torch.empty((8, total), dtype=torch.int32, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    pb = _lib.PromptBuildArgs(
+        n_variants=n, n_perms=20, d_cells=table.d_cells.data_ptr(), d_grid_off=table.d_grid_off.data_ptr(),
+        d_grid_h=table.d_grid_h.data_ptr(), d_grid_w=table.d_grid_w.data_ptr(), d_tpl_off=table.d_tpl_off.data_ptr(),
+        d_tpl_grid=table.d_tpl_grid.data_ptr(), d_perm_lut=table.d_perm_lut.data_ptr(),
+        d_var_template=d_tpl.data_ptr(), d_var_dihedral=d_dih.data_ptr(), d_var_perm=d_perm.data_ptr(),
+        d_var_tok_off=d_off.data_ptr(), d_var_seq=None, d_token_ids=out[0].data_ptr(), d_pos_xyz=out[1:4].data_ptr(),
+        d_seq=out[4].data_ptr(), d_kv_slot=out[5].data_ptr(), d_kv_count=out[6].data_ptr(),
+        d_kv_row=out[7].data_ptr(), d_status=status.data_ptr())
+    build_ms = timed(lambda: _lib.check(lib.arcb_build_prompts(C.byref(pb), stream)))
+    assert int(status.item()) == 0
+    build_bytes = total * 32          # token id, 3 position words, seq, slot, count, scratch row
+    del out
+    # canonicalisation: well-formed generations (a transformed grid, END, then END padding)
+    rng = np.random.default_rng(0)
+    max_new = 931
+    rows = np.full((n, max_new), 13, np.int32)
+    for i in range(0, n, 160):
+        g = rng.integers(0, 10, size=(int(rng.integers(1, 31)), int(rng.integers(1, 31))))
+        t = np.concatenate([np.concatenate([r, [11]]) for r in g] + [[13]]).astype(np.int32)
+        rows[i: i + 160, : len(t)] = t
+    d_rows = torch.from_numpy(rows).to(dev)
+    rec = torch.empty((n, fanout.RECORD_BYTES), dtype=torch.uint8, device=dev)
+    d_test = up(table.tpl_test_grid[vt.template])
+    ca = _lib.CandidateArgs(
+        n_rows=n, max_new=max_new, d_tokens=d_rows.data_ptr(), d_row_dihedral=d_dih.data_ptr(),
+        d_row_perm=d_perm.data_ptr(), d_perm_lut=table.d_perm_lut.data_ptr(), n_perms=20,
+        d_row_test_grid=d_test.data_ptr(), d_cells=table.d_cells.data_ptr(), d_grid_off=table.d_grid_off.data_ptr(),
+        d_grid_h=table.d_grid_h.data_ptr(), d_grid_w=table.d_grid_w.data_ptr(), d_records=rec.data_ptr())
+    canon_ms = timed(lambda: _lib.check(lib.arcb_canonicalize_candidates(C.byref(ca), stream)))
+    canon_bytes = n * (max_new * 4 + fanout.RECORD_BYTES)
+    print(json.dumps({"profile": "fan-out kernels", "tasks": len(tasks), "variants": n, "prompt_tokens": total,
+                      "table_upload_and_shapes_s": t_table,
+                      "build_prompts": {"ms": build_ms, "bytes_written": build_bytes, "gbs": build_bytes / build_ms / 1e6},
+                      "canonicalize": {"ms": canon_ms, "bytes_read_plus_written": canon_bytes,
+                                       "gbs": canon_bytes / canon_ms / 1e6}}))
+
+
 def run_ours(args, rank, world, local_rank):
     from mdlarc_scale_b200 import _lib
     from mdlarc_scale_b200.engine import Engine, chunk_rows, plan_prefill
@@ -474,6 +549,8 @@ def main():
                     help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
     ap.add_argument("--profile-prefill", type=int, default=0, metavar="PAIRS",
                     help="only time the prefill of ~64k tokens of prompts with PAIRS 30x30 train pairs")
+    ap.add_argument("--profile-fanout", type=int, default=0, metavar="TASKS",
+                    help="only time the fan-out kernels for TASKS synthetic tasks x 8 x 20 variants")
     ap.add_argument("--profile-long", type=int, default=0, metavar="SEQS",
                     help="only run one wave of SEQS 10 247-token prompts + --max-new tokens (long-context decode)")
     ap.add_argument("--max-new", type=int, default=MAX_NEW,
@@ -496,6 +573,9 @@ def main():
         return
     if args.profile_long > 0:
         profile_long_context(args)
+        return
+    if args.profile_fanout > 0:
+        profile_fanout(args)
         return
     run_ours(args, rank, world, local_rank)
 

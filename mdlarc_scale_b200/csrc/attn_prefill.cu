@@ -281,24 +281,32 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         // ---- packed-half path: scores are packed to half2 as they leave TMEM; max, scale-and-shift,
         // exp2 (two per special-function instruction) and the row sum run on half2 ----
         __half2 h2[64];
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          uint32_t s0[32], s1[32];
-          tmem_ld_32x32(t_s + cc * 64, s0);
-          tmem_ld_32x32(t_s + cc * 64 + 32, s1);
+        {
+          // all four loads in flight before the first wait: the TMEM read latency is paid once per tile
+          uint32_t s0[32], s1[32], s2[32], s3[32];
+          tmem_ld_32x32(t_s, s0);
+          tmem_ld_32x32(t_s + 32, s1);
+          tmem_ld_32x32(t_s + 64, s2);
+          tmem_ld_32x32(t_s + 96, s3);
           tmem_wait_ld_dep(s0);
           tmem_wait_ld_dep(s1);
+          tmem_wait_ld_dep(s2);
+          tmem_wait_ld_dep(s3);
           if (!full) {
 #pragma unroll
             for (int i = 0; i < 32; ++i) {
-              if (cc * 64 + i >= n_valid) s0[i] = 0xff800000u;       // -inf: exp2 gives exactly 0
-              if (cc * 64 + 32 + i >= n_valid) s1[i] = 0xff800000u;
+              if (i >= n_valid) s0[i] = 0xff800000u;       // -inf: exp2 gives exactly 0
+              if (32 + i >= n_valid) s1[i] = 0xff800000u;
+              if (64 + i >= n_valid) s2[i] = 0xff800000u;
+              if (96 + i >= n_valid) s3[i] = 0xff800000u;
             }
           }
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            h2[cc * 32 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-            h2[cc * 32 + 16 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+            h2[(i >> 1)] = __floats2half2_rn(__uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
+            h2[16 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
+            h2[32 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
+            h2[48 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
           }
         }
         // S is in registers: the tensor core may overwrite it with the next tile's scores

@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(BUILD_THREADS) build_prompts_kernel(arcb_promp
       int j = 0;
       while (j + 1 < n_grids && s_start[j + 1] <= t) ++j;
       const int h = s_h[j], w = s_w[j];
-      const int th = swap ? w : h, tw = swap ? h : w;
+      const int tw = swap ? h : w;
       const bool is_out = j & 1;
       const int seg_len = s_start[j + 1] - s_start[j];
       int u = t - s_start[j];
@@ -104,16 +104,83 @@ __global__ void __launch_bounds__(BUILD_THREADS) build_prompts_kernel(arcb_promp
 }
 
 constexpr int CAND_THREADS = 128;
+constexpr int CAND_PER = 8;   // consecutive tokens per thread: 128 x 8 = 1024 >= ARCB_CANDIDATE_MAX_CELLS
+
+// Block-wide exclusive scans over one value per thread (CAND_THREADS threads); `total` receives the
+// reduction over all threads.  s_part: 4 ints of shared scratch (one per warp).
+__device__ __forceinline__ int block_excl_sum(int v, int* s_part, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  __syncthreads();                     // previous use of s_part is over
+  if (lane == 31) s_part[warp] = inc;
+  __syncthreads();
+  int base = 0;
+  total = 0;
+#pragma unroll
+  for (int w = 0; w < CAND_THREADS / 32; ++w) {
+    if (w < warp) base += s_part[w];
+    total += s_part[w];
+  }
+  return base + inc - v;
+}
+__device__ __forceinline__ int block_excl_max(int v, int* s_part, int& total) {   // identity: -1
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc = max(inc, t);
+  }
+  int excl = __shfl_up_sync(0xffffffffu, inc, 1);
+  if (lane == 0) excl = -1;
+  __syncthreads();
+  if (lane == 31) s_part[warp] = inc;
+  __syncthreads();
+  int base = -1;
+  total = -1;
+#pragma unroll
+  for (int w = 0; w < CAND_THREADS / 32; ++w) {
+    if (w < warp) base = max(base, s_part[w]);
+    total = max(total, s_part[w]);
+  }
+  return max(base, excl);
+}
+__device__ __forceinline__ int block_min(int v, int* s_part) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = min(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return min(min(s_part[0], s_part[1]), min(s_part[2], s_part[3]));
+}
+__device__ __forceinline__ int block_max(int v, int* s_part) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xffffffffu, v, o));
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return max(max(s_part[0], s_part[1]), max(s_part[2], s_part[3]));
+}
 
 // One CTA per generated row.  The grid is read after the last IO_SEP and before the first END
 // (src/inference.py:906-915, src/data.py:95-117); rows end at NEWLINE, empty rows are dropped,
-// START is ignored (src/data.py:54-72).  A serial scan by one thread keeps those rules literal;
-// the transform back and the record write are done by the whole CTA.
+// START is ignored (src/data.py:54-72).  Those sequential rules are evaluated with block-wide
+// scans over the row's tokens (8 consecutive tokens per thread):
+//   P[i]     colour cells before token i             (prefix sum)
+//   L[i]     P at the last NEWLINE before i, or -1   (prefix maximum; P never decreases)
+//   a NEWLINE at i closes a row iff P[i] > max(L[i], 0); a cell's column is P[i] - max(L[i], 0) and
+//   its row the number of closing NEWLINEs before it, so cell i lands at raw[P[i]] and the grid is
+//   rectangular iff every closed row (and a trailing unclosed one) has the first row's width.
 __global__ void __launch_bounds__(CAND_THREADS) canonicalize_kernel(arcb_candidate_args a) {
-  __shared__ int s_tok[ARCB_CANDIDATE_MAX_CELLS];
+  __shared__ int s_tok[CAND_THREADS * CAND_PER];
   __shared__ unsigned char s_raw[ARCB_CANDIDATE_MAX_CELLS];
   __shared__ unsigned char s_inv[10];
-  __shared__ int s_hdr[4];   // status, h, w, n_tokens
+  __shared__ int s_part[CAND_THREADS / 32];
   __shared__ int s_same;
   const int row = blockIdx.x;
   if (row >= a.n_rows) return;
@@ -125,7 +192,8 @@ __global__ void __launch_bounds__(CAND_THREADS) canonicalize_kernel(arcb_candida
     return;
   }
   const int* toks = a.d_tokens + (long long)row * a.max_new;
-  for (int i = threadIdx.x; i < a.max_new; i += CAND_THREADS) s_tok[i] = toks[i];
+  for (int i = threadIdx.x; i < CAND_THREADS * CAND_PER; i += CAND_THREADS)
+    s_tok[i] = i < a.max_new ? toks[i] : TOK_END;
   if (threadIdx.x < 10) {
     // inverse of the old -> new colour map
     const int perm = a.d_row_perm ? a.d_row_perm[row] : 0;
@@ -134,29 +202,74 @@ __global__ void __launch_bounds__(CAND_THREADS) canonicalize_kernel(arcb_candida
   }
   if (threadIdx.x == 0) s_same = 1;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int n = a.max_new;  // tokens before the first END
-    for (int i = 0; i < a.max_new; ++i) if (s_tok[i] == TOK_END) { n = i; break; }
-    int start = 0;      // the prompt ends with IO_SEP, so the grid starts at 0 unless the model emits another
-    for (int i = 0; i < n; ++i) if (s_tok[i] == TOK_IO_SEP) start = i + 1;
-    int status, h = 0, w = 0;
-    if (start >= n) status = 0;
-    else {
-      int cur = 0, cells = 0; bool jag = false;
-      for (int i = start; i < n; ++i) {
-        const int t = s_tok[i];
-        if (t == TOK_NEWLINE) {
-          if (cur > 0) { if (h == 0) w = cur; else if (cur != w) jag = true; ++h; cur = 0; }
-        } else if (t >= 0 && t < 10) { s_raw[cells++] = (unsigned char)t; ++cur; }
-      }
-      if (cur > 0) { if (h == 0) w = cur; else if (cur != w) jag = true; ++h; }
-      status = (h > 0 && !jag) ? 1 : 2;
-      if (status != 1) h = w = 0;
-    }
-    s_hdr[0] = status; s_hdr[1] = h; s_hdr[2] = w; s_hdr[3] = min(n + 1, a.max_new);
+  const int i0 = threadIdx.x * CAND_PER;
+  int tk[CAND_PER];
+#pragma unroll
+  for (int k = 0; k < CAND_PER; ++k) tk[k] = s_tok[i0 + k];
+  // n: tokens before the first END; start: one past the last IO_SEP before it (the prompt ends with
+  // IO_SEP, so the grid starts at 0 unless the model emits another)
+  int v = a.max_new;
+#pragma unroll
+  for (int k = CAND_PER - 1; k >= 0; --k) if (tk[k] == TOK_END) v = i0 + k;
+  const int n = min(block_min(v, s_part), a.max_new);
+  v = -1;
+#pragma unroll
+  for (int k = 0; k < CAND_PER; ++k) if (i0 + k < n && tk[k] == TOK_IO_SEP) v = i0 + k;
+  const int start = block_max(v, s_part) + 1;
+  // per-token classes inside [start, n)
+  bool is_col[CAND_PER], is_nl[CAND_PER];
+  int ncol = 0;
+#pragma unroll
+  for (int k = 0; k < CAND_PER; ++k) {
+    const bool in = i0 + k >= start && i0 + k < n;
+    is_col[k] = in && tk[k] >= 0 && tk[k] < 10;
+    is_nl[k] = in && tk[k] == TOK_NEWLINE;
+    ncol += is_col[k];
   }
+  int n_cells;
+  int P = block_excl_sum(ncol, s_part, n_cells);      // colours before this thread's first token
+  int Pk[CAND_PER];
+  int vmax = -1;
+#pragma unroll
+  for (int k = 0; k < CAND_PER; ++k) {
+    Pk[k] = P;
+    if (is_nl[k]) vmax = P;                            // P never decreases: the last NEWLINE holds the maximum
+    P += is_col[k];
+  }
+  int last_nl_P;                                       // P at the row's last NEWLINE, or -1
+  int L = block_excl_max(vmax, s_part, last_nl_P);
+  int neff = 0, jag_w_lo = 1 << 30, jag_w_hi = -1;
+  bool eff[CAND_PER];
+#pragma unroll
+  for (int k = 0; k < CAND_PER; ++k) {
+    const int row_start = max(L, 0);
+    eff[k] = is_nl[k] && Pk[k] > row_start;
+    if (eff[k]) {
+      const int w = Pk[k] - row_start;                 // width of the row this NEWLINE closes
+      jag_w_lo = min(jag_w_lo, w);
+      jag_w_hi = max(jag_w_hi, w);
+      ++neff;
+    }
+    if (is_nl[k]) L = Pk[k];
+  }
+  int n_closed;
+  block_excl_sum(neff, s_part, n_closed);
+  const int w_lo = block_min(jag_w_lo, s_part), w_hi = block_max(jag_w_hi, s_part);
+  const int trailing = n_cells - max(last_nl_P, 0);   // cells after the last NEWLINE
+  int status, h = 0, w = 0;
+  if (start >= n) status = 0;
+  else {
+    h = n_closed + (trailing > 0 ? 1 : 0);
+    if (n_closed > 0) w = w_lo; else w = trailing;
+    const bool jag = (n_closed > 0 && (w_lo != w_hi || (trailing > 0 && trailing != w_lo)));
+    status = (h > 0 && !jag) ? 1 : 2;
+    if (status != 1) h = w = 0;
+  }
+  // cells in row-major order
+#pragma unroll
+  for (int k = 0; k < CAND_PER; ++k)
+    if (is_col[k]) s_raw[Pk[k]] = (unsigned char)tk[k];
   __syncthreads();
-  const int status = s_hdr[0], h = s_hdr[1], w = s_hdr[2];
   // input-copy flag: the grid as generated against the task's test input (src/voting.py:92)
   int tg = (status == 1 && a.d_row_test_grid) ? a.d_row_test_grid[row] : -1;
   if (tg >= 0) {
@@ -172,17 +285,17 @@ __global__ void __launch_bounds__(CAND_THREADS) canonicalize_kernel(arcb_candida
   if (threadIdx.x == 0) {
     rec->status = (uint8_t)status;
     rec->input_copy = (uint8_t)(tg >= 0 && s_same);
-    rec->n_tokens = (uint16_t)s_hdr[3];
+    rec->n_tokens = (uint16_t)min(n + 1, a.max_new);
   }
   // back to the task's orientation: apply DIHEDRAL_TRANSFORMS[inverse(d)] (src/voting.py:16-31)
   const int inv_d = (d == 1) ? 3 : (d == 3) ? 1 : d;
   const bool swap = dihedral_swaps(inv_d);
   const int ch = swap ? w : h, cw = swap ? h : w;
   if (threadIdx.x == 0) { rec->h = (uint16_t)ch; rec->w = (uint16_t)cw; }
-  const int n_cells = h * w;
+  const int n_out = h * w;
   for (int i = threadIdx.x; i < ARCB_CANDIDATE_MAX_CELLS; i += CAND_THREADS) {
     unsigned char out = 0;
-    if (i < n_cells) {
+    if (i < n_out) {
       const int r = i / cw, c = i - r * cw;
       out = s_inv[s_raw[dihedral_src(inv_d, r, c, h, w)]];
     }

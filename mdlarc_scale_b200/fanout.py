@@ -18,7 +18,7 @@ import torch
 
 from . import _lib
 from .data import TRANSPOSING, as_rect_array, generate_color_permutations
-from .engine import PrefillPlan, _qblocks
+from .engine import PrefillPlan
 
 RECORD_BYTES = 944
 MAX_CELLS = 936
@@ -153,9 +153,13 @@ class TaskTable:
             d_kv_slot=out[5].data_ptr(), d_kv_count=out[6].data_ptr(), d_kv_row=out[7].data_ptr(),
             d_status=status.data_ptr())
         _lib.check(lib.arcb_build_prompts(C.byref(args), torch.cuda.current_stream(dev).cuda_stream))
-        seq_of_tok = np.repeat(np.arange(n), lens)
-        qb0, qbn = _qblocks(seq_of_tok)
-        qb_kv0 = tok_off[:-1][seq_of_tok[qb0]] if len(qb0) else np.zeros(0, np.int32)
+        # query blocks of at most 256 consecutive rows of one sequence, from the lengths alone
+        nblk = (lens + 255) // 256
+        blk_seq = np.repeat(np.arange(n), nblk)
+        blk_k = np.arange(int(nblk.sum())) - np.repeat(np.cumsum(nblk) - nblk, nblk)
+        qb0 = (tok_off[:-1][blk_seq] + 256 * blk_k).astype(np.int32)
+        qbn = np.minimum(256, lens[blk_seq] - 256 * blk_k).astype(np.int32)
+        qb_kv0 = tok_off[:-1][blk_seq].astype(np.int32)
         zeros = np.zeros(n, np.int32)
         plan = PrefillPlan(
             n_tokens=total, token_ids=out[0, :total], pos_xyz=out[1:4].reshape(-1)[: 3 * total].view(total, 3),
