@@ -235,9 +235,13 @@ class Session:
             _lib.check(lib.arcb_session_create(eng._handle, C.byref(desc), C.byref(self._handle)))
 
     def close(self) -> None:
+        """Destroy the library session and give the cache and workspace back to torch's allocator
+        (work already queued on the stream still completes first: the allocator is stream-ordered)."""
         if getattr(self, "_handle", None) and self._handle.value:
             self.eng.lib.arcb_session_destroy(self._handle)
             self._handle = C.c_void_p()
+        self.kv_cache = None
+        self.workspace = None
 
     def __del__(self):
         try:

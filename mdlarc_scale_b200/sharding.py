@@ -210,7 +210,8 @@ def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, eng
         for p in plans:
             check_status(p)
         table.canonicalize(tokens, vt, idx, local[w0: w0 + n])   # straight into the gather slice
-        sess.close()
+        sess.close()      # frees the wave's cache before the next wave allocates its own
+        del sess, plans, tokens
     return gather_records(rec, rank, world, vt.length, group)
 
 
