@@ -557,6 +557,12 @@ def main():
                     help="tokens generated per sequence (the workload uses 931; smaller only for profiling)")
     args = ap.parse_args()
     MAX_NEW = args.max_new
+    if args.gpus > 1 and "WORLD_SIZE" not in os.environ:
+        # started without a launcher: re-run under torchrun, one rank per GPU, rendezvous on 127.0.0.1
+        port = 29500 + os.getpid() % 1000
+        os.execvp(sys.executable, [sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
+                                   f"--nproc-per-node={args.gpus}", "--master-addr", "127.0.0.1",
+                                   "--master-port", str(port), os.path.abspath(__file__), *sys.argv[1:]])
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
