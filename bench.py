@@ -460,6 +460,9 @@ def run_ours(args, rank, world, local_rank):
         if rank == 0:
             print(json.dumps({"profiling_run": True, "value": world * args.steps * B * MAX_NEW / dt,
                               "attn_gbs": attn_gbs, "prefill_tok_s": prefill_tok_s, "gpu_launches": launches}))
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
         return
     host = []
     for ids, pos, mask in batches:
