@@ -31,13 +31,15 @@ ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
 MAX_NEW = 931
+MAX_NEW_FULL = 931   # the configurations' budget (MAX_NEW may be lowered for profiling runs)
 KV_POSITIONS = 1536
 MODEL_SIZE = "large"
-# DRAM traffic of the decode-attention kernel relative to its algorithmic bytes, from the ncu
-# capture summarised in profiles/attn_stream_kernel_ncu_full.md (256 sequences x 1000 cached
-# positions: 1311.40 MB read + 3.6 MB written per launch for 1310.72 MB algorithmic); traffic grows
-# in proportion to the cached positions, so a full-size launch is scaled by its algorithmic bytes.
+# DRAM traffic of the decode-attention kernel relative to its algorithmic bytes, measured with one
+# ncu capture of the standalone kernel on 256 sequences x 1000 cached positions (1311.40 MB read +
+# 3.6 MB written per launch for 1310.72 MB algorithmic); traffic grows in proportion to the cached
+# positions, so a full-size launch is scaled by its algorithmic bytes.
 ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0033
+LINEAR_FLOP_PER_TOKEN = 469.9e6          # large model: 2 x matmul parameters
 
 
 def measured_peaks():
@@ -46,6 +48,15 @@ def measured_peaks():
         d = json.loads(p.read_text())
         return float(d["hbm_gbs"]), "measured"
     return 6650.0, "fallback"
+
+
+def measured_tensor_peaks():
+    """(burst, sustained) dense bf16 TFLOP/s and whether they are this pool's measured figures."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["bf16_tflops"]), float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return 1590.0, 1400.0, "fallback"
 
 
 class ClockSampler:
@@ -109,19 +120,61 @@ def model_state():
 
 
 # ---------------------------------------------------------------------------
-# CPU baseline / reference arm: the oracle port of generate_output on the host cores
+# CPU baseline / reference arm: the reference project's own generate_output (its files copied to
+# oracle/_ref by oracle/make_ref.py) on the host cores; the oracle port only when they are absent
 # ---------------------------------------------------------------------------
+_REF_MODEL = None
+
+
+def _reference_model():
+    """The reference TinyTransformer (large) holding this benchmark's seeded weights, or None."""
+    global _REF_MODEL
+    if _REF_MODEL is None:
+        from oracle import make_ref  # the timed CPU baseline IS the reference / its port
+        if not make_ref.available():
+            _REF_MODEL = False
+        else:
+            mods = make_ref.load_reference_modules("arcref")
+            cfg_d, sd = model_state()
+            model = mods["transformer"].create_large_model(max_seq_len=cfg_d["max_seq_len"])
+            model.load_state_dict(sd, strict=True)
+            model.eval()
+            _REF_MODEL = (model, mods["inference"].generate_output)
+    return _REF_MODEL or None
+
+
 def cpu_generate_sample(n_seqs: int, n_steps: int, seed: int):
-    from oracle import arc_model as om  # the timed CPU baseline IS the oracle port
-    cfg_d, sd = model_state()
-    cfg = om.Config(**cfg_d)
+    """Prefill + n_steps greedy tokens of n_seqs sequences of the benchmark's generator on the host
+    cores, fp32.  Returns (tokens/s, seconds, kind, mean cached length over the decode steps)."""
     ids, pos, mask = make_batch(seed, n_seqs)
+    ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
+    ref = _reference_model()
     t0 = time.perf_counter()
-    r = om.generate(sd, cfg, torch.from_numpy(ids), torch.from_numpy(pos), None, torch.from_numpy(mask),
-                    max_new_tokens=n_steps, stop_on_end=False)
+    if ref is not None:
+        model, generate_output = ref
+        with torch.no_grad():
+            out = generate_output(model, ids_t, pos_t, None, mask_t, max_new_tokens=n_steps, stop_on_end=False)
+        gen = out.shape[1] - ids.shape[1]
+        kind = "reference"
+    else:
+        from oracle import arc_model as om
+        cfg_d, sd = model_state()
+        r = om.generate(sd, om.Config(**cfg_d), ids_t, pos_t, None, mask_t, max_new_tokens=n_steps,
+                        stop_on_end=False)
+        gen = r.tokens.shape[1] - ids.shape[1]
+        kind = "port"
     dt = time.perf_counter() - t0
-    gen = r.tokens.shape[1] - ids.shape[1]
-    return n_seqs * gen / dt, dt
+    mean_cache = float(mask.sum(axis=1).mean()) + gen / 2.0
+    return n_seqs * gen / dt, dt, kind, mean_cache
+
+
+def _cpu_sample_text(n_seqs, n_steps, kind, mean_cache, dt=None):
+    what = ("the reference's own generate_output (src/inference.py), unmodified" if kind == "reference"
+            else "oracle port of generate_output")
+    txt = (f"{n_seqs} sequences of the same generator x (prefill + {n_steps} greedy tokens), fp32, {what}; "
+           f"mean cached length {mean_cache:.0f} positions (the GPU arm: 1024 sequences x {MAX_NEW} tokens at "
+           f"mean cached length ~{252 + MAX_NEW // 2})")
+    return txt + (f"; {dt:.1f} s wall" if dt is not None else "")
 
 
 def run_reference(args, rank):
@@ -132,14 +185,12 @@ def run_reference(args, rank):
     n_seqs, n_steps = args.cpu_seqs, args.cpu_steps
     for i in range(args.warmup):
         cpu_generate_sample(2, 4, 1000 + i)
-    vals, times = [], []
+    vals, times, kind, mean_cache = [], [], "port", 0.0
     for i in range(args.steps):
-        v, dt = cpu_generate_sample(n_seqs, n_steps, 2000 + i)
+        v, dt, kind, mean_cache = cpu_generate_sample(n_seqs, n_steps, 2000 + i)
         vals.append(v)
         times.append(dt)
     value = float(np.mean(vals))
-    sample = (f"{n_seqs} sequences of the same generator, prefill + {n_steps} greedy tokens each per step, "
-              f"fp32, oracle port of generate_output (tokens / wall time incl. prefill)")
     line = {
         "impl": "reference", "metric": "generated tokens/s", "value": value, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
@@ -148,8 +199,8 @@ def run_reference(args, rank):
         "config": {"workload": "cfg4-large-decode", "model": MODEL_SIZE, "sequences_per_gpu_per_step": args.batch,
                    "new_tokens": MAX_NEW, "kv_positions": KV_POSITIONS, "stop_on_end": False,
                    "note": "CPU arm: each step is a bounded sample of this workload (see cpu_baseline.sample)"},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": _cpu_sample_text(n_seqs, n_steps, kind, mean_cache)},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -186,7 +237,8 @@ def attention_roofline(engine, session, lens0: np.ndarray, n_layers_sampled: int
             e1.synchronize()
             times.append(e0.elapsed_time(e1) / 1e3)
             bytes_.append(algo)
-    gbs = float(np.mean([b / t for b, t in zip(bytes_, times)]) / 1e9)
+    # achieved = sum of bytes / sum of time, so achieved x ms_per_launch = algorithmic_bytes_per_launch
+    gbs = float(np.sum(bytes_) / np.sum(times) / 1e9)
     return gbs, float(np.mean(times) * 1e3), float(np.mean(bytes_))
 
 
@@ -375,6 +427,86 @@ def profile_fanout(args):
                                        "gbs": canon_bytes / canon_ms / 1e6}}))
 
 
+def prefill_heavy_sample(engine, dev, repeats: int = 3):
+    """One prefill call of the prefill-heavy large configuration: 6 prompts of 5 pairs of 30x30 grids
+    plus a 30x30 test input (10 247 tokens each, 61 482 packed tokens), timed with CUDA events.
+    Algorithmic FLOPs: 469.9 MFLOP per token for the linear layers + 2 * d * L * len^2 per sequence for
+    causal attention (only the causal half is counted)."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import plan_prefill
+    from mdlarc_scale_b200.inference import pad_prompts
+    tasks = synthetic.capped_tasks(3, 6, 5, 5, 30, 30, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    lens = mask.sum(axis=1)
+    sess = engine.new_session(len(prompts), int(lens.max()) + 8, 8, 65536, stop_on_end=False)
+    plan = plan_prefill(ids, pos, mask, np.arange(len(prompts))).to(dev)
+    ms = []
+    for i in range(1 + repeats):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        sess.prefill(plan, None)
+        e1.record()
+        e1.synchronize()
+        if i > 0:
+            ms.append(e0.elapsed_time(e1))
+    sess.poll()
+    sess.close()
+    t = float(np.mean(ms)) / 1e3
+    ntok = int(lens.sum())
+    flop = ntok * LINEAR_FLOP_PER_TOKEN + float((2.0 * engine.d_model * engine.n_layers * lens.astype(np.float64) ** 2).sum())
+    burst, sustained, kind = measured_tensor_peaks()
+    return {"workload": "cfg3-large-prefill: one call of 6 prompts x 10247 tokens (5 pairs of 30x30 + test input)",
+            "tokens": ntok, "ms": t * 1e3, "ms_all": [round(x, 3) for x in ms], "tokens_per_s_per_gpu": ntok / t,
+            "algorithmic_tflop": flop / 1e12, "tflops": flop / t / 1e12,
+            "frac_of_bf16_burst_peak": flop / t / 1e12 / burst, "frac_of_bf16_sustained_peak": flop / t / 1e12 / sustained,
+            "peak_kind": kind, "peaks_tflops": {"burst": burst, "sustained": sustained}}
+
+
+def vote_pipeline_sample(rank, world, dev, dist, n_tasks: int = 8, perms: int = 20):
+    """The voting configuration's multi-GPU pipeline on a bounded sample: medium model, n_tasks x 8
+    dihedral x perms colour permutations variants dealt to the ranks by length-sorted round-robin,
+    prompts built and candidates canonicalised on the device, ONE all-gather of the candidate
+    records, AAIVR vote on every rank.  The vote digest must not depend on the number of ranks."""
+    import hashlib
+    from mdlarc_scale_b200 import fanout, sharding, synthetic
+    from mdlarc_scale_b200.engine import Engine
+    cfg, sd = synthetic.seeded_weights("medium", 0, 8.0)
+    engine = Engine(sd, cfg, dev)
+    tasks = synthetic.capped_tasks(2, n_tasks, 2, 4, 1, 30, 2048)
+    table = fanout.TaskTable(tasks, dev, num_color_perms=perms)
+    vt = table.variants()
+    torch.cuda.synchronize(dev)
+    if dist is not None:
+        dist.barrier()
+    timing = {}
+    t0 = time.perf_counter()
+    records = sharding.generate_sharded_records(table, vt, MAX_NEW_FULL, rank, world, engine, timing=timing)
+    torch.cuda.synchronize(dev)
+    t_gen = time.perf_counter() - t0
+    t1 = time.perf_counter()
+    votes = fanout.vote_records(records, vt, top_k=2, seed=7)
+    t_vote = time.perf_counter() - t1
+    digest = hashlib.sha256(json.dumps(sorted((list(k), v) for k, v in votes.items())).encode()).hexdigest()
+    gen = fanout.record_fields(records)[4].astype(np.int64)
+    per_rank = [int((vt.length[idx].astype(np.int64) + gen[idx]).sum()) for idx in sharding.assign(vt.length, world)]
+    ag_ms = float(timing.get("all_gather_ms", 0.0))
+    if dist is not None:
+        t = torch.tensor([t_gen, ag_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        t_gen, ag_ms = float(t[0].item()), float(t[1].item())
+    engine.close()
+    torch.cuda.empty_cache()
+    return {"workload": f"cfg2-medium sample: {n_tasks} tasks x 8 dihedral x {perms} colour permutations = {len(vt)} variants, "
+                        f"prompts <= 2048 tokens, greedy to END or {MAX_NEW_FULL} tokens",
+            "n_gpus": world, "variants": int(len(vt)), "generate_and_gather_s": t_gen,
+            "all_gather_ms": ag_ms, "all_gather_bytes": int(timing.get("gather_bytes", 0)),
+            "vote_s": t_vote, "generated_tokens": int(gen.sum()), "generated_tokens_per_s": float(gen.sum()) / t_gen,
+            "rank_tokens_max_over_mean": max(per_rank) / (sum(per_rank) / len(per_rank)),
+            "tasks_with_votes": sum(1 for v in votes.values() if v), "votes_sha256": digest}
+
+
+
 def run_ours(args, rank, world, local_rank):
     from mdlarc_scale_b200 import _lib
     from mdlarc_scale_b200.engine import Engine, chunk_rows, plan_prefill
@@ -495,6 +627,17 @@ def run_ours(args, rank, world, local_rank):
 
     dt = max_over_ranks(dt)
     e2e_dt = max_over_ranks(e2e_dt)
+    # outside every timed region: the prefill-heavy configuration's prefill call (rank 0) and the voting
+    # configuration's sharded pipeline (all ranks)
+    del host
+    torch.cuda.empty_cache()
+    extras = {}
+    if not args.no_extras:
+        if rank == 0:
+            extras["prefill_heavy"] = prefill_heavy_sample(engine, dev)
+        engine.close()
+        torch.cuda.empty_cache()
+        extras["vote_pipeline"] = vote_pipeline_sample(rank, world, dev, dist)
     gen_tokens = world * args.steps * B * MAX_NEW
     clocks = sampler.summary()
     if rank == 0:
@@ -523,13 +666,13 @@ def run_ours(args, rank, world, local_rank):
                                              "gbs": live_bytes / live_ms / 1e6}},
             "prefill": {"tokens_per_s_per_gpu": prefill_tok_s, "tokens_per_step": prefill_tokens // args.steps},
         }
+        line.update(extras)
         if not args.no_cpu and world == 1:
             torch.set_num_threads(os.cpu_count() or 1)
-            v, cdt = cpu_generate_sample(args.cpu_seqs, args.cpu_steps, 777)
+            v, cdt, kind, mean_cache = cpu_generate_sample(args.cpu_seqs, args.cpu_steps, 777)
             line["cpu_baseline"] = {
-                "value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                "sample": f"{args.cpu_seqs} sequences x (prefill + {args.cpu_steps} greedy tokens), fp32 oracle port, "
-                          f"{cdt:.1f} s wall"}
+                "value": v, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+                "sample": _cpu_sample_text(args.cpu_seqs, args.cpu_steps, kind, mean_cache, cdt)}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
@@ -548,6 +691,8 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=112)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the prefill-heavy prefill call and the sharded vote pipeline sample")
     ap.add_argument("--profile-attn", type=int, default=0, metavar="T",
                     help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
     ap.add_argument("--profile-prefill", type=int, default=0, metavar="PAIRS",

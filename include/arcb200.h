@@ -14,7 +14,9 @@
  *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
  *   - return value: 0 = ok, <0 = argument/state error (ARCB_E_*), >0 = a
  *     cudaError_t / CUresult value; arcb_last_error() gives a message;
- *   - no exceptions cross the boundary, no global state besides the handles.
+ *   - no exceptions cross the boundary; besides the handles the library keeps only
+ *     per-device constants looked up once (SM count, resident cluster pairs, the
+ *     address of the built-in scratch of arcb_op_decode_attention_static).
  */
 #ifndef ARCB200_H
 #define ARCB200_H
@@ -109,6 +111,14 @@ int arcb_engine_destroy(arcb_engine* eng);
 int arcb_engine_load_tensor(arcb_engine* eng, int32_t kind, int32_t layer, const float* d_src,
                             int64_t numel, void* stream);
 
+/* 16-bit saturation warnings.  GEMM operands are IEEE half by default: a value beyond +-65504 on
+ * its way into q16 / k16 / v16 / the SwiGLU activations is clamped, and an attention score that
+ * overflows half in the flash prefill kernel becomes infinite.  Neither faults; each occurrence
+ * adds one to a device counter that this call reads (after synchronising `stream`) and, with
+ * reset != 0, clears.  A non-zero count means the model's activations do not fit the half format
+ * and ARCB_ACT_BF16 should be used instead.  No counterpart in the reference (which runs bf16). */
+int arcb_engine_saturation_count(arcb_engine* eng, int64_t* count, int32_t reset, void* stream);
+
 /* ---- session: one batch of sequences sharing a static KV cache --------- */
 
 /* StaticKVCache + GridStateUpdater + the per-call tensors of generate_output
@@ -137,17 +147,25 @@ typedef struct arcb_session_desc {
   /* Sampling (src/inference.py:575-583, 612-620): temperature <= 0 = greedy argmax.  Otherwise the
    * (constrained) logits are divided by max(temperature, 1e-6), optionally cut to the top_k largest
    * (0 = all), soft-maxed and sampled by inverse CDF with the uniform number
-   * u = splitmix64(sample_seed, row, generated index) >> 40 scaled to [0, 1): a counter-based
+   * u = splitmix64(sample_seed, stream id, generated index) >> 40 scaled to [0, 1): a counter-based
    * stream, reproducible for a seed and independent of batch shape (torch.multinomial's stream
-   * cannot be reproduced on the device). */
+   * cannot be reproduced on the device).  The stream id of a row is d_sample_stream[row] when that
+   * array is given, else the row index; a caller that spreads one job over several sessions or
+   * ranks passes a job-wide id per row (e.g. the variant number) so that no two sequences of the
+   * job share a stream and the draw does not depend on how the job was split. */
   float temperature;
   int32_t top_k;
   uint64_t sample_seed;
+  const int32_t* d_sample_stream; /* optional int32 [B] */
 } arcb_session_desc;
 
 int64_t arcb_session_workspace_bytes(const arcb_engine* eng, int32_t n_seqs,
                                      int32_t max_prefill_tokens, int32_t attn_splits);
 int64_t arcb_kv_cache_bytes(const arcb_engine* eng, int32_t n_seqs, int32_t t_max);
+/* Creating a session launches nothing: the session's device state (inside d_workspace) is cleared
+ * by the session's FIRST arcb_prefill, on that call's stream, so a workspace recycled from an
+ * earlier session is ordered after whatever that stream still has queued on it.  Use one stream
+ * (or your own ordering) for all calls of a session. */
 int arcb_session_create(arcb_engine* eng, const arcb_session_desc* desc, arcb_session** out);
 int arcb_session_destroy(arcb_session* s);
 

@@ -26,7 +26,7 @@ EXPORTS = [
     "arcb_last_error", "arcb_device_ok", "arcb_engine_create", "arcb_engine_destroy",
     "arcb_engine_load_tensor", "arcb_session_workspace_bytes", "arcb_kv_cache_bytes",
     "arcb_session_create", "arcb_session_destroy", "arcb_prefill", "arcb_decode",
-    "arcb_session_poll", "arcb_session_attention_probe", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
+    "arcb_session_poll", "arcb_engine_saturation_count", "arcb_session_attention_probe", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
     "arcb_op_gemm_residual",
     "arcb_attn_scratch_bytes", "arcb_op_decode_attention", "arcb_op_decode_attention_static",
     "arcb_op_head", "arcb_build_prompts", "arcb_canonicalize_candidates",
@@ -54,6 +54,7 @@ class SessionDesc(C.Structure):
         ("d_palette_mask", C.c_void_p), ("d_target_shape", C.c_void_p),
         ("palette_penalty", C.c_float), ("shape_penalty", C.c_float), ("disallow_token_mask", C.c_uint32),
         ("temperature", C.c_float), ("top_k", C.c_int32), ("sample_seed", C.c_uint64),
+        ("d_sample_stream", C.c_void_p),
     ]
 
 
@@ -131,6 +132,7 @@ def load() -> C.CDLL:
     lib.arcb_decode.argtypes = [vp, i32, vp]
     lib.arcb_session_poll.argtypes = [vp, C.POINTER(i32), C.POINTER(i32), vp]
     lib.arcb_session_attention_probe.argtypes = [vp, C.POINTER(C.c_float)]
+    lib.arcb_engine_saturation_count.argtypes = [vp, C.POINTER(i64), i32, vp]
     lib.arcb_build_prompts.argtypes = [C.POINTER(PromptBuildArgs), vp]
     lib.arcb_canonicalize_candidates.argtypes = [C.POINTER(CandidateArgs), vp]
     lib.arcb_launch_count.restype = i64

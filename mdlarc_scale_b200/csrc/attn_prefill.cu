@@ -15,10 +15,19 @@
 // than 8 (in log2 units), so p <= 256 stays well inside the 16-bit range and the accumulated O
 // rarely needs rescaling; when it does, the row's thread rescales O in TMEM before releasing P.
 // The final 1/l normalisation makes the result independent of m_ref.
+// Scores stay fp32 until the row's reference maximum has been subtracted (t = s * 1/sqrt(64) *
+// log2(e) - m_ref <= 8): only that shifted value is rounded to half, so neither the size of q.k nor
+// the 16-bit range limits what the softmax can represent.
+// In the packed-half path POLY of every 8 exp2 pairs are evaluated on the FMA pipe (Cody-Waite
+// split + cubic polynomial + exponent insertion, all on packed halves) instead of the
+// special-function unit, which is the busiest pipe of this kernel; the two kinds are interleaved
+// so that both pipes work at once.
 // The two groups run out of phase: the tensor core works on one Q tile while the other group's
 // threads do exponentials.  Rows carry their own visible-key count (causal AND key padding as a
 // prefix length), so no mask tensor exists.  Q, K, V and P share one 16-bit format (kind::f16
 // needs equal A/B formats).  Every mbarrier wait is bounded.
+#include <cstdlib>
+
 #include "attn_prefill.cuh"
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
@@ -38,6 +47,9 @@ constexpr int TMEM_P = 384;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr int N_THREADS = 320;
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
+#ifndef ARCB_FLASH_POLY_DEFAULT
+#define ARCB_FLASH_POLY_DEFAULT 2
+#endif
 
 // MN-major operand tile [K rows of 128 bytes][64 elements], 128-byte swizzle: 8-row groups are
 // 1024 bytes apart along K (stride byte offset); a single 64-element group along MN.
@@ -75,6 +87,56 @@ __device__ __forceinline__ __half2 ex2_half2(__half2 x) {
   return *reinterpret_cast<__half2*>(&yi);
 }
 __device__ __forceinline__ uint32_t h2_bits(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 h2_from_bits(uint32_t b) { return *reinterpret_cast<__half2*>(&b); }
+
+__device__ __forceinline__ float max3_f32(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+// half2(s0 * c + m, s1 * c + m): one two-wide fp32 fused multiply-add, then one rounding to half
+__device__ __forceinline__ __half2 shift_pack_half2(uint32_t s0, uint32_t s1, uint64_t c2, uint64_t m2) {
+  uint64_t sp, tp;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(sp) : "r"(s0), "r"(s1));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(tp) : "l"(sp), "l"(c2), "l"(m2));
+  float t0, t1;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(tp));
+  return __floats2half2_rn(t0, t1);
+}
+
+// 2^t for two packed halves, t <= 8, WITHOUT the special-function unit (9 FMA/ALU-pipe instructions
+// per pair).  t is clamped to -15 (anything below yields exactly 0, so masked -inf scores work),
+// n = round(t) comes from adding 1536 (ulp 1 at that magnitude; the sum's bit pattern is
+// 0x6600 + n), f = t - n lies in [-0.5, 0.5] exactly, 2^f ~ 1 + f (c1 + f (c2 + f c3)) (max
+// relative error 5.4e-4 in half arithmetic, about one half ulp) and 2^n is built in the exponent
+// field: bits = (n + 15) << 10 per half.  One 32-bit multiply-add makes both halves' scale at
+// once: (r * 1024 + C) leaves (n + 15) << 10 in each 16-bit lane for n in [-15, 16] because the
+// low lane's spill into the high lane plus its carry is the constant 0x198.
+__device__ __forceinline__ __half2 ex2_poly_half2(__half2 t) {
+  t = __hmax2(t, h2_from_bits(0xCB80CB80u));                   // max(t, -15)
+  const __half2 magic = h2_from_bits(0x66006600u);             // 1536
+  const __half2 r = __hadd2(t, magic);
+  const __half2 f = __hsub2(t, __hsub2(r, magic));
+  __half2 q = __hfma2(h2_from_bits(0x2B1B2B1Bu), f, h2_from_bits(0x33C233C2u));
+  q = __hfma2(q, f, h2_from_bits(0x398C398Cu));
+  const __half2 s = h2_from_bits(h2_bits(r) * 1024u + 0x3A683C00u);  // 2^n
+  return __hfma2(q, __hmul2(f, s), s);
+}
+// which of the 8 exp2 pairs of a group go to the polynomial (spread out so the pipes interleave)
+template <int POLY>
+__device__ __forceinline__ constexpr bool ex2_on_fma(int e) {
+  return POLY >= 8 ? true
+       : POLY == 4 ? (e & 1) == 1
+       : POLY == 3 ? (e == 1 || e == 4 || e == 6)
+       : POLY == 2 ? (e == 3 || e == 7)
+       : POLY == 1 ? (e == 5)
+       : false;
+}
 
 struct Bars {
   uint32_t q, kv_full, kv_empty, s[2], p[2], o[2], sfree[2];
@@ -86,8 +148,10 @@ struct Bars {
 // (A third form, fp32 scores with a 3-input max and fp32 exp2, packing only the probabilities,
 // issues fewer instructions but needs all 128 scores live in fp32: it spilled and measured
 // 66.8 ms against 62.6 ms for form 1 on 61 482 tokens of 10 247-token prompts.)
-template <int SOFTMAX>
-__global__ void __launch_bounds__(N_THREADS, 1)
+// 320 threads x 200 registers fill the register file (a launch bound of 320 threads would be rounded
+// up to 384 by the compiler and cap the kernel at 168 registers, which spills).
+template <int SOFTMAX, int POLY>
+__global__ void __maxnreg__(200)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, AttnPrefillArgs a, uint32_t idesc_qk,
                     uint32_t idesc_pv) {
@@ -278,74 +342,57 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const int n_valid = min(max(my_cnt - j * BKV, 0), BKV);   // visible keys of this row in the tile
       const bool full = __all_sync(0xffffffffu, n_valid == BKV);
       if constexpr (SOFTMAX == 1) {
-        // ---- packed-half path: scores are packed to half2 as they leave TMEM; max, scale-and-shift,
-        // exp2 (two per special-function instruction) and the row sum run on half2 ----
-        __half2 h2[64];
-        {
-          // all four loads in flight before the first wait: the TMEM read latency is paid once per tile
-          uint32_t s0[32], s1[32], s2[32], s3[32];
-          tmem_ld_32x32(t_s, s0);
-          tmem_ld_32x32(t_s + 32, s1);
-          tmem_ld_32x32(t_s + 64, s2);
-          tmem_ld_32x32(t_s + 96, s3);
-          tmem_wait_ld_dep(s0);
-          tmem_wait_ld_dep(s1);
-          tmem_wait_ld_dep(s2);
-          tmem_wait_ld_dep(s3);
-          if (!full) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (i >= n_valid) s0[i] = 0xff800000u;       // -inf: exp2 gives exactly 0
-              if (32 + i >= n_valid) s1[i] = 0xff800000u;
-              if (64 + i >= n_valid) s2[i] = 0xff800000u;
-              if (96 + i >= n_valid) s3[i] = 0xff800000u;
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            h2[(i >> 1)] = __floats2half2_rn(__uint_as_float(s0[i]), __uint_as_float(s0[i + 1]));
-            h2[16 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s1[i]), __uint_as_float(s1[i + 1]));
-            h2[32 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s2[i]), __uint_as_float(s2[i + 1]));
-            h2[48 + (i >> 1)] = __floats2half2_rn(__uint_as_float(s3[i]), __uint_as_float(s3[i + 1]));
-          }
-        }
+        // ---- packed-half path.  The row maximum and the shift t = s * c - m_ref are computed in fp32
+        // (3-input max, packed two-wide fused multiply-add), t is rounded to half once (|t| is small
+        // where the probability is large, so the rounding costs little), and exp2 and the row sum run
+        // on packed halves ----
+        uint32_t sv[4][32];
+        // all four loads in flight before the first wait: the TMEM read latency is paid once per tile
+        tmem_ld_32x32(t_s, sv[0]);
+        tmem_ld_32x32(t_s + 32, sv[1]);
+        tmem_ld_32x32(t_s + 64, sv[2]);
+        tmem_ld_32x32(t_s + 96, sv[3]);
+        tmem_wait_ld_dep(sv[0]);
+        tmem_wait_ld_dep(sv[1]);
+        tmem_wait_ld_dep(sv[2]);
+        tmem_wait_ld_dep(sv[3]);
         // S is in registers: the tensor core may overwrite it with the next tile's scores
         tc_fence_before();
         mbar_arrive(B.sfree[grp]);
-        __half2 mx2[4] = {h2[0], h2[1], h2[2], h2[3]};
+        if (!full) {
 #pragma unroll
-        for (int i = 4; i < 64; i += 4) {
-          mx2[0] = __hmax2(mx2[0], h2[i]);
-          mx2[1] = __hmax2(mx2[1], h2[i + 1]);
-          mx2[2] = __hmax2(mx2[2], h2[i + 2]);
-          mx2[3] = __hmax2(mx2[3], h2[i + 3]);
+          for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i >= n_valid) sv[c][i] = 0xff800000u;   // -inf: exp2 gives exactly 0
         }
-        const __half2 mxx = __hmax2(__hmax2(mx2[0], mx2[1]), __hmax2(mx2[2], mx2[3]));
-        const float mx = fmaxf(__low2float(mxx), __high2float(mxx)) * sc;
+        float mx4[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          mx4[c] = fmaxf(__uint_as_float(sv[c][0]), __uint_as_float(sv[c][1]));
+#pragma unroll
+          for (int i = 2; i < 32; i += 2) mx4[c] = max3_f32(mx4[c], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 1]));
+        }
+        const float mx = fmaxf(max3_f32(mx4[0], mx4[1], mx4[2]), mx4[3]) * sc;
         float alpha = 1.f;
         if (mx > m_ref + RESCALE_THRESHOLD) {  // also the first visible tile (m_ref = -inf)
-          const float m_new = __half2float(__float2half_rn(mx));  // the value the half2 math will use
-          alpha = (m_ref == -INFINITY) ? 0.f : ex2_fast(m_ref - m_new);
-          m_ref = m_new;
+          alpha = (m_ref == -INFINITY) ? 0.f : ex2_fast(m_ref - mx);
+          m_ref = mx;
         }
         l *= alpha;
-        if (j > 0) {
-          // PV(j-1) must have retired: it reads the P buffer written below and updates O
-          bool good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
-          if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-          ok = __all_sync(0xffffffffu, good);
-          if (!ok) break;
-          tc_fence_after();
-        }
-        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) rescale_o(alpha);
         const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
-        const __half2 sc2 = __float2half2_rn(sc), nm2 = __float2half2_rn(-m_safe);
+        const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-m_safe, -m_safe);
+        __half2 h2[64];
         float lsum = 0.f;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {  // 8 half2 = 16 columns = two 16-byte chunks of the P row
+        for (int g = 0; g < 8; ++g) {  // 8 half2 = 16 keys = two 16-byte chunks of the P row
           __half2 p[8];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) p[e] = ex2_half2(__hfma2(h2[g * 8 + e], sc2, nm2));
+          for (int e = 0; e < 8; ++e) {
+            const int k = g * 8 + e;                    // keys 2k, 2k + 1
+            const __half2 t = shift_pack_half2(sv[k >> 4][(2 * k) & 31], sv[k >> 4][((2 * k) & 31) + 1], sc2, nm2);
+            p[e] = ex2_on_fma<POLY>(e) ? ex2_poly_half2(t) : ex2_half2(t);
+          }
           const __half2 t = __hadd2(__hadd2(__hadd2(p[0], p[1]), __hadd2(p[2], p[3])),
                                     __hadd2(__hadd2(p[4], p[5]), __hadd2(p[6], p[7])));
           lsum += __low2float(t) + __high2float(t);
@@ -353,6 +400,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           for (int e = 0; e < 8; ++e) h2[g * 8 + e] = p[e];   // keys 16 g .. 16 g + 15 = P columns 8 g .. 8 g + 7
         }
         l += lsum;
+        if (j > 0) {
+          // PV(j-1) must have retired before P is overwritten and O rescaled; the exponentials above
+          // needed neither, so they overlap that product
+          bool good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
+          if (!good) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+          ok = __all_sync(0xffffffffu, good);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) rescale_o(alpha);
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t pk[32];
@@ -494,10 +551,36 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
 
 bool arcb_attn_prefill_available() { return true; }
 
+namespace {
+
+// exp2 pairs (of every 8) evaluated on the FMA pipe by the packed-half kernel.  The default is the
+// measured optimum on B200; ARCB_FLASH_POLY=0..4 overrides it (read once) for A/B timing.
+int flash_poly_share() {
+  static const int v = [] {
+    const char* e = getenv("ARCB_FLASH_POLY");
+    if (e && e[0] >= '0' && e[0] <= '4' && e[1] == 0) return e[0] - '0';
+    return ARCB_FLASH_POLY_DEFAULT;
+  }();
+  return v;
+}
+
+template <int SOFTMAX, int POLY>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(attn_prefill_kernel<SOFTMAX, POLY>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              SMEM_BYTES);
+}
+
+}  // namespace
+
 int arcb_attn_prefill_init() {
-  cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-  if (e != cudaSuccess) return (int)e;
-  return (int)cudaFuncSetAttribute(attn_prefill_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  cudaError_t e;
+  if ((e = set_smem_attr<0, 0>()) != cudaSuccess) return (int)e;
+  if ((e = set_smem_attr<1, 0>()) != cudaSuccess) return (int)e;
+  if ((e = set_smem_attr<1, 1>()) != cudaSuccess) return (int)e;
+  if ((e = set_smem_attr<1, 2>()) != cudaSuccess) return (int)e;
+  if ((e = set_smem_attr<1, 3>()) != cudaSuccess) return (int)e;
+  if ((e = set_smem_attr<1, 4>()) != cudaSuccess) return (int)e;
+  return 0;
 }
 
 int arcb_launch_attn_prefill(const AttnPrefillArgs& a, cudaStream_t stream) {
@@ -515,8 +598,20 @@ int arcb_launch_attn_prefill(const AttnPrefillArgs& a, cudaStream_t stream) {
   const uint32_t idesc_qk = umma_idesc_f16(BQ, BKV, fmt, fmt, 0, 0);
   const uint32_t idesc_pv = umma_idesc_f16(BQ, HD, fmt, fmt, 0, 1);  // B = V is MN-major
   dim3 grid(a.n_qblocks, a.n_heads);
-  if (a.act_f16) attn_prefill_kernel<1><<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv);
-  else attn_prefill_kernel<0><<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv);
+#define ARCB_LAUNCH_FLASH(SM, PL) \
+  attn_prefill_kernel<SM, PL><<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv)
+  if (!a.act_f16) {
+    ARCB_LAUNCH_FLASH(0, 0);
+  } else {
+    switch (flash_poly_share()) {
+      case 0: ARCB_LAUNCH_FLASH(1, 0); break;
+      case 1: ARCB_LAUNCH_FLASH(1, 1); break;
+      case 2: ARCB_LAUNCH_FLASH(1, 2); break;
+      case 3: ARCB_LAUNCH_FLASH(1, 3); break;
+      default: ARCB_LAUNCH_FLASH(1, 4); break;
+    }
+  }
+#undef ARCB_LAUNCH_FLASH
   arcb_count_launch(1);
   return (int)cudaGetLastError();
 }

@@ -26,6 +26,13 @@ __device__ __forceinline__ void arcb_set_error(int* err, int code) {
   if (err) atomicCAS(err, 0, code);
 }
 
+// Word 1 of the error block counts 16-bit saturations: values the half format cannot hold that were
+// clamped to +-65504 on their way into a GEMM operand (or a score that overflowed to infinity).
+// It is a warning, not an error: the run continues, the host reads and clears the count.
+__device__ __forceinline__ void arcb_count_saturation(int* err) {
+  if (err) atomicAdd(err + 1, 1);
+}
+
 // ---- 16-bit activation formats -------------------------------------------
 // act_f16 != 0: IEEE half (values clamped to the finite half range), else bfloat16.
 
@@ -38,6 +45,12 @@ __device__ __forceinline__ uint32_t pack2_act(float a, float b, int act_f16) {
   }
   __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// pack2_act that also reports a clamp (half format only) in the saturation counter
+__device__ __forceinline__ uint32_t pack2_act_chk(float a, float b, int act_f16, int* err) {
+  if (act_f16 && fmaxf(fabsf(a), fabsf(b)) > 65504.f) arcb_count_saturation(err);
+  return pack2_act(a, b, act_f16);
 }
 
 __device__ __forceinline__ float2 unpack2_act(uint32_t v, int act_f16) {

@@ -97,6 +97,10 @@ struct arcb_session {
   // event pair recorded (as graph nodes) around the layer-0 decode-attention launch of every replay
   cudaEvent_t probe_begin = nullptr, probe_end = nullptr;
   bool probe_recorded = false;
+  // the integer state block is cleared by the first arcb_prefill, on that call's stream
+  int* state_ints = nullptr;
+  size_t n_state_ints = 0;
+  bool state_cleared = false;
 };
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -341,10 +345,14 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
   st.temperature = dsc->temperature;
   st.top_k = dsc->top_k;
   st.sample_seed = dsc->sample_seed;
+  st.sample_stream = dsc->d_sample_stream;
   st.err = e->d_err;
-  cudaError_t r = cudaMemset(ints, 0, w.n_int * 4);
-  if (r != cudaSuccess) { delete s; return fail_cuda(r, "cudaMemset(session state)"); }
-  r = cudaStreamCreateWithFlags(&s->capture_stream, cudaStreamNonBlocking);
+  // No device work here: the state block may be a recycled allocation whose previous user still
+  // has kernels queued on the caller's stream, so it is cleared by the first arcb_prefill, in
+  // stream order.
+  s->state_ints = ints;
+  s->n_state_ints = w.n_int;
+  cudaError_t r = cudaStreamCreateWithFlags(&s->capture_stream, cudaStreamNonBlocking);
   if (r != cudaSuccess) { delete s; return fail_cuda(r, "cudaStreamCreate"); }
   if (cudaEventCreate(&s->probe_begin) != cudaSuccess || cudaEventCreate(&s->probe_end) != cudaSuccess) {
     cudaGetLastError();
@@ -457,6 +465,10 @@ extern "C" int arcb_prefill(arcb_session* s, const arcb_prefill_args* a, void* s
   cudaStream_t stream = (cudaStream_t)stream_v;
   arcb_engine* e = s->eng;
   const arcb_config& c = e->cfg;
+  if (!s->state_cleared) {
+    CK(cudaMemsetAsync(s->state_ints, 0, s->n_state_ints * 4, stream));
+    s->state_cleared = true;
+  }
   const bool use_ex = c.use_example_embedding && a->d_example_ids;
   if (a->n_first > 0) {
     if (s->graph_exec && s->use_examples != use_ex) {  // the recorded step baked the other choice in
@@ -554,6 +566,17 @@ extern "C" int arcb_session_poll(arcb_session* s, int32_t* n_finished, int32_t* 
     snprintf(buf, sizeof buf, "device error word = %d", err);
     return fail(ARCB_E_DEVICE, buf);
   }
+  return ARCB_OK;
+}
+
+extern "C" int arcb_engine_saturation_count(arcb_engine* e, int64_t* count, int32_t reset, void* stream_v) {
+  if (!e || !count) return fail(ARCB_E_ARG, "null argument");
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  int n = 0;
+  CK(cudaMemcpyAsync(&n, e->d_err + 1, 4, cudaMemcpyDeviceToHost, stream));
+  if (reset) CK(cudaMemsetAsync(e->d_err + 1, 0, 4, stream));
+  CK(cudaStreamSynchronize(stream));
+  *count = n;
   return ARCB_OK;
 }
 

@@ -33,7 +33,7 @@ struct GemmEpilogue {
   int t_max, n_heads, d_model, n_seqs;
   const float* rope;  // cos_x | sin_x | cos_y | sin_y | cos_z | sin_z
   int max_x, max_y, max_z;
-  int* err;
+  int* err;           // error word; word 1 counts 16-bit saturations
 };
 
 struct RopeRow {
@@ -98,8 +98,8 @@ __device__ __forceinline__ void epi_qkv_quad(const GemmEpilogue& e, const RopeRo
   }
   if (sec == 0) {
     uint2 pk;
-    pk.x = pack2_act(v.x, v.y, e.act_f16);
-    pk.y = pack2_act(v.z, v.w, e.act_f16);
+    pk.x = pack2_act_chk(v.x, v.y, e.act_f16, e.err);
+    pk.y = pack2_act_chk(v.z, v.w, e.act_f16, e.err);
     *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(e.out16) + (size_t)m * d + c) = pk;
   } else {
     if (r.kv_row >= 0) {
@@ -113,8 +113,8 @@ __device__ __forceinline__ void epi_qkv_quad(const GemmEpilogue& e, const RopeRo
     if (r.row16 >= 0) {
       uint16_t* base16 = reinterpret_cast<uint16_t*>((sec == 1) ? e.k16 : e.v16);
       uint2 pk;
-      pk.x = pack2_act(v.x, v.y, e.act_f16);
-      pk.y = pack2_act(v.z, v.w, e.act_f16);
+      pk.x = pack2_act_chk(v.x, v.y, e.act_f16, e.err);
+      pk.y = pack2_act_chk(v.z, v.w, e.act_f16, e.err);
       *reinterpret_cast<uint2*>(base16 + (size_t)r.row16 * d + c) = pk;
     }
   }
@@ -166,8 +166,8 @@ __device__ __forceinline__ void epi_qkv_chunk32(const GemmEpilogue& e, const Rop
     uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(e.out16) + (size_t)m * d + c);
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      dst[q] = make_uint4(pack2_act(v[8 * q], v[8 * q + 1], e.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], e.act_f16),
-                          pack2_act(v[8 * q + 4], v[8 * q + 5], e.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], e.act_f16));
+      dst[q] = make_uint4(pack2_act_chk(v[8 * q], v[8 * q + 1], e.act_f16, e.err), pack2_act_chk(v[8 * q + 2], v[8 * q + 3], e.act_f16, e.err),
+                          pack2_act_chk(v[8 * q + 4], v[8 * q + 5], e.act_f16, e.err), pack2_act_chk(v[8 * q + 6], v[8 * q + 7], e.act_f16, e.err));
     return;
   }
   if (r.kv_row >= 0) {
@@ -183,8 +183,8 @@ __device__ __forceinline__ void epi_qkv_chunk32(const GemmEpilogue& e, const Rop
                                           (size_t)r.row16 * d + c);
 #pragma unroll
     for (int q = 0; q < 4; ++q)
-      dst[q] = make_uint4(pack2_act(v[8 * q], v[8 * q + 1], e.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], e.act_f16),
-                          pack2_act(v[8 * q + 4], v[8 * q + 5], e.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], e.act_f16));
+      dst[q] = make_uint4(pack2_act_chk(v[8 * q], v[8 * q + 1], e.act_f16, e.err), pack2_act_chk(v[8 * q + 2], v[8 * q + 3], e.act_f16, e.err),
+                          pack2_act_chk(v[8 * q + 4], v[8 * q + 5], e.act_f16, e.err), pack2_act_chk(v[8 * q + 6], v[8 * q + 7], e.act_f16, e.err));
   }
 }
 
@@ -216,7 +216,7 @@ __device__ __forceinline__ void epi_swiglu_quad(const GemmEpilogue& e, int m, in
   }
   const int j = (n >> 7) * 64 + (n & 127);
   uint2 pk;
-  pk.x = pack2_act(silu_f(g.x) * u.x, silu_f(g.y) * u.y, e.act_f16);
-  pk.y = pack2_act(silu_f(g.z) * u.z, silu_f(g.w) * u.w, e.act_f16);
+  pk.x = pack2_act_chk(silu_f(g.x) * u.x, silu_f(g.y) * u.y, e.act_f16, e.err);
+  pk.y = pack2_act_chk(silu_f(g.z) * u.z, silu_f(g.w) * u.w, e.act_f16, e.err);
   *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(e.out16) + (size_t)m * (e.N >> 1) + j) = pk;
 }

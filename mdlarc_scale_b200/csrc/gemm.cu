@@ -126,8 +126,8 @@ __device__ __forceinline__ void epilogue_swiglu_tma(const GemmEpilogue& ep, cons
           g.x += bg.x; g.y += bg.y; g.z += bg.z; g.w += bg.w;
           u.x += bu.x; u.y += bu.y; u.z += bu.z; u.w += bu.w;
         }
-        w[2 * h] = pack2_act(silu_f(g.x) * u.x, silu_f(g.y) * u.y, ep.act_f16);
-        w[2 * h + 1] = pack2_act(silu_f(g.z) * u.z, silu_f(g.w) * u.w, ep.act_f16);
+        w[2 * h] = pack2_act_chk(silu_f(g.x) * u.x, silu_f(g.y) * u.y, ep.act_f16, ep.err);
+        w[2 * h + 1] = pack2_act_chk(silu_f(g.z) * u.z, silu_f(g.w) * u.w, ep.act_f16, ep.err);
       }
       *reinterpret_cast<uint4*>(my_row + (((c * 4 + k) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -189,15 +189,15 @@ __device__ __forceinline__ void epilogue_qkv_tma(const GemmEpilogue& ep, const R
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<uint4*>(my_row + (((half * 4 + q) ^ sw) << 4)) =
-              make_uint4(pack2_act(v[8 * q], v[8 * q + 1], ep.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], ep.act_f16),
-                         pack2_act(v[8 * q + 4], v[8 * q + 5], ep.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], ep.act_f16));
+              make_uint4(pack2_act_chk(v[8 * q], v[8 * q + 1], ep.act_f16, ep.err), pack2_act_chk(v[8 * q + 2], v[8 * q + 3], ep.act_f16, ep.err),
+                         pack2_act_chk(v[8 * q + 4], v[8 * q + 5], ep.act_f16, ep.err), pack2_act_chk(v[8 * q + 6], v[8 * q + 7], ep.act_f16, ep.err));
       } else if (sec > 0 && row_ok && rr.row16 >= 0) {
         uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>((sec == 1) ? ep.k16 : ep.v16) +
                                               (size_t)rr.row16 * d + c + half * 32);
 #pragma unroll
         for (int q = 0; q < 4; ++q)
-          dst[q] = make_uint4(pack2_act(v[8 * q], v[8 * q + 1], ep.act_f16), pack2_act(v[8 * q + 2], v[8 * q + 3], ep.act_f16),
-                              pack2_act(v[8 * q + 4], v[8 * q + 5], ep.act_f16), pack2_act(v[8 * q + 6], v[8 * q + 7], ep.act_f16));
+          dst[q] = make_uint4(pack2_act_chk(v[8 * q], v[8 * q + 1], ep.act_f16, ep.err), pack2_act_chk(v[8 * q + 2], v[8 * q + 3], ep.act_f16, ep.err),
+                              pack2_act_chk(v[8 * q + 4], v[8 * q + 5], ep.act_f16, ep.err), pack2_act_chk(v[8 * q + 6], v[8 * q + 7], ep.act_f16, ep.err));
       }
     }
     if (staged) {
@@ -774,8 +774,19 @@ static cudaError_t set_tc_smem_attr() {
                               TcCfg<256>::SMEM_BYTES + epi_stage_bytes<MODE>());
 }
 
-static int g_num_sms = 0;
-static int g_max_pairs = 0;  // 2-CTA clusters that can be resident at once
+// Per-device launch limits, filled by arcb_gemm_init() for the device that is current then and
+// read for the device that is current at launch (a process may drive several GPUs).
+constexpr int MAX_DEVICES = 64;
+static int g_num_sms[MAX_DEVICES] = {0};
+static int g_max_pairs[MAX_DEVICES] = {0};  // 2-CTA clusters that can be resident at once
+
+static int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return 0;
+  return dev;
+}
+static int num_sms() { const int n = g_num_sms[current_device_slot()]; return n > 0 ? n : 148; }
+static int max_pairs() { return g_max_pairs[current_device_slot()]; }
 
 template <int MODE>
 static cudaError_t set_tc2_smem_attr() {
@@ -806,12 +817,15 @@ int arcb_gemm_init() {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<EPI_RESID>, &cfg) == cudaSuccess) g_max_pairs = n;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc2_kernel<EPI_RESID>, &cfg) == cudaSuccess)
+      g_max_pairs[current_device_slot()] = n;
     else cudaGetLastError();
   }
   int dev = 0;
   if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
-  if ((e = cudaDeviceGetAttribute(&g_num_sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+  int sms = 0;
+  if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+  if (dev >= 0 && dev < MAX_DEVICES) g_num_sms[dev] = sms;
   return get_encode_fn() ? 0 : -100;
 }
 
@@ -820,7 +834,7 @@ static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtens
                       const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + BN - 1) / BN, tiles_m = (ep.M + TC_BM - 1) / TC_BM;
   const int tiles = tiles_n * tiles_m;
-  const int sms = g_num_sms > 0 ? g_num_sms : 148;
+  const int sms = num_sms();
   const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
   gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, TC_THREADS, TcCfg<BN>::SMEM_BYTES + epi_stage_bytes<MODE>(),
                              stream>>>(ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
@@ -831,13 +845,14 @@ static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
                        const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + 255) / 256, tiles_m = (ep.M + 255) / 256;
   const int tiles = tiles_n * tiles_m;
-  const int pairs = tiles < g_max_pairs ? tiles : g_max_pairs;
+  const int mp = max_pairs();
+  const int pairs = tiles < mp ? tiles : mp;
   const uint32_t idesc = umma_idesc_f16(256, 256, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
   gemm_tc2_kernel<MODE><<<2 * pairs, TC_THREADS, Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>(), stream>>>(
       ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
 }
 
-int arcb_gemm_max_pairs() { return g_max_pairs; }
+int arcb_gemm_max_pairs() { return max_pairs(); }
 
 template <int MODE>
 static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue& ep, int K,
@@ -845,15 +860,15 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
   const int M = ep.M, N = ep.N;
   if (use_tc) {
     // 128 x 256 tiles (one CTA per SM, persistent) unless that leaves most SMs without a tile
-    const int sms = g_num_sms > 0 ? g_num_sms : 148;
+    const int sms = num_sms();
     const int tiles256 = ((N + 255) / 256) * ((M + TC_BM - 1) / TC_BM);
     // the QKV epilogue of the 256-column kernels needs tiles that stay inside one of the q / k / v sections
     const bool allow256 = !(MODE == EPI_QKV_ROPE && ep.d_model % 256 != 0);
     const bool wide = allow256 && tiles256 * 10 >= sms * 7;
     // 256 x 256 tiles on CTA pairs when there are enough of them to occupy the machine
     const int tiles2 = ((N + 255) / 256) * ((M + 255) / 256);
-    const bool pair = allow256 && g_max_pairs > 0 &&
-                      (tc_variant == 2 || (tc_variant == 0 && tiles2 * 10 >= g_max_pairs * 7));
+    const int mp = max_pairs();
+    const bool pair = allow256 && mp > 0 && (tc_variant == 2 || (tc_variant == 0 && tiles2 * 10 >= mp * 7));
     CUtensorMap ta, tb;
     int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
     if (r) return 1000 + r;

@@ -230,8 +230,10 @@ head_kernel(HeadArgs a, DecodeState st) {
         p[v] = (rank < kk) ? __expf((adj[v] - bv2) * inv_t) : 0.f;
         total += p[v];
       }
-      // counter-based uniform number: splitmix64 of (seed, row, generated index)
-      unsigned long long z = st.sample_seed + 0x9E3779B97F4A7C15ull * (unsigned long long)(b + 1) +
+      // counter-based uniform number: splitmix64 of (seed, stream id, generated index)
+      const unsigned long long sid = st.sample_stream ? (unsigned long long)(unsigned int)st.sample_stream[b]
+                                                      : (unsigned long long)b;
+      unsigned long long z = st.sample_seed + 0x9E3779B97F4A7C15ull * (sid + 1) +
                              0xD1B54A32D192ED03ull * (unsigned long long)(out_idx + 1);
       z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
       z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;

@@ -26,6 +26,7 @@ struct DecodeState {
   float temperature;
   int top_k;
   unsigned long long sample_seed;
+  const int* sample_stream;   // optional [B]: random-stream id of each row (default: the row index)
   int* err;
 };
 

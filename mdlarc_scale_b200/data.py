@@ -183,6 +183,19 @@ def generate_color_permutations(n_perms: int, seed: int = 42) -> np.ndarray:
     return perms
 
 
+def apply_color_perm_to_tokens(tokens, perm):
+    """Token tensor with colours 0-9 mapped through ``perm`` (old -> new) and the special tokens
+    left alone (src/data.py:281-298).  Works on torch tensors and numpy arrays."""
+    if hasattr(tokens, "clone"):
+        out = tokens.clone()
+    else:
+        out = np.array(tokens, copy=True)
+        perm = np.asarray(perm)
+    is_colour = tokens < 10
+    out[is_colour] = perm[tokens[is_colour]]
+    return out
+
+
 def inverse_color_perm(perm) -> np.ndarray:
     perm = np.asarray(perm)
     inv = np.zeros_like(perm)

@@ -28,6 +28,18 @@ def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def sample_uniform(seed: int, stream: int, index: int) -> float:
+    """The uniform number in [0, 1) that the token-picking kernel draws for generated token ``index``
+    of the row whose random-stream id is ``stream`` (host mirror of the device's counter-based
+    generator: splitmix64 of seed + golden * (stream + 1) + c * (index + 1), top 24 bits)."""
+    m = (1 << 64) - 1
+    z = (seed + 0x9E3779B97F4A7C15 * (stream + 1) + 0xD1B54A32D192ED03 * (index + 1)) & m
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+    z ^= z >> 31
+    return (z >> 40) / 16777216.0
+
+
 def rope_tables(head_dim: int, max_x: int, max_y: int, max_z: int, base: float) -> dict[str, torch.Tensor]:
     """cos/sin tables of RotaryEmbedding3D (src/transformer.py:87-126), fp32 on the CPU.
 
@@ -139,6 +151,15 @@ class Engine:
         except Exception:
             pass
 
+    def saturation_count(self, reset: bool = True) -> int:
+        """Values clamped to the half range (or attention scores that overflowed it) since the last
+        reset: a warning that the model's activations do not fit IEEE half (use act_format="bf16")."""
+        n = C.c_int64(0)
+        with torch.cuda.device(self.device):
+            _lib.check(self.lib.arcb_engine_saturation_count(self._handle, C.byref(n), int(bool(reset)),
+                                                             _stream_ptr(self.device)))
+        return int(n.value)
+
     # ------------------------------------------------------------------
     def kv_bytes_per_position(self) -> int:
         return self.n_layers * 2 * self.d_model * 2
@@ -147,9 +168,10 @@ class Engine:
                     stop_on_end: bool = True, attn_splits: int = 0, forced: torch.Tensor | None = None,
                     want_step_logits: bool = False, out_tokens: torch.Tensor | None = None,
                     constraints: dict | None = None, temperature: float = 0.0, top_k: int = 0,
-                    sample_seed: int = 0) -> "Session":
+                    sample_seed: int = 0, sample_stream=None) -> "Session":
         return Session(self, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end, attn_splits,
-                       forced, want_step_logits, out_tokens, constraints, temperature, top_k, sample_seed)
+                       forced, want_step_logits, out_tokens, constraints, temperature, top_k, sample_seed,
+                       sample_stream)
 
 
 _ENGINES: "weakref.WeakKeyDictionary" = weakref.WeakKeyDictionary()
@@ -176,7 +198,7 @@ class Session:
 
     def __init__(self, eng: Engine, n_seqs, t_max, max_new, max_prefill_tokens, stop_on_end,
                  attn_splits, forced, want_step_logits, out_tokens=None, constraints=None,
-                 temperature=0.0, top_k=0, sample_seed=0):
+                 temperature=0.0, top_k=0, sample_seed=0, sample_stream=None):
         self.eng = eng
         self.n_seqs, self.t_max, self.max_new = int(n_seqs), int(t_max), int(max_new)
         self.max_prefill_tokens = int(max_prefill_tokens)
@@ -219,6 +241,13 @@ class Session:
             shp_pen = float(constraints.get("shape_penalty", 2.0))
             for t in constraints.get("disallow_tokens", ()):
                 disallow |= 1 << int(t)
+        # random-stream id of each row when sampling (default: the row index); a job split over
+        # several sessions / ranks passes job-wide ids so that no two of its sequences share a stream
+        self.sample_stream = None
+        if sample_stream is not None:
+            self.sample_stream = torch.as_tensor(np.asarray(sample_stream, dtype=np.int64) & 0x7FFFFFFF).to(
+                device=dev, dtype=torch.int32).contiguous()
+            assert tuple(self.sample_stream.shape) == (self.n_seqs,)
         desc = _lib.SessionDesc(
             n_seqs=self.n_seqs, t_max=self.t_max, max_new=self.max_new,
             max_prefill_tokens=self.max_prefill_tokens, attn_splits=int(attn_splits),
@@ -229,7 +258,8 @@ class Session:
             d_step_logits=_ptr(self.step_logits),
             d_palette_mask=_ptr(self.palette_mask), d_target_shape=_ptr(self.target_shape),
             palette_penalty=pal_pen, shape_penalty=shp_pen, disallow_token_mask=disallow,
-            temperature=float(temperature), top_k=int(top_k or 0), sample_seed=int(sample_seed) & (2 ** 64 - 1))
+            temperature=float(temperature), top_k=int(top_k or 0), sample_seed=int(sample_seed) & (2 ** 64 - 1),
+            d_sample_stream=_ptr(self.sample_stream))
         self._handle = C.c_void_p()
         with torch.cuda.device(dev):
             _lib.check(lib.arcb_session_create(eng._handle, C.byref(desc), C.byref(self._handle)))

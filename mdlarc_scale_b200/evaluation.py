@@ -5,16 +5,21 @@ generation + voting, with the reference's signatures and result dictionaries
 
 Two ways of spreading the work over ranks, behind the same ``rank`` / ``world_size`` arguments:
 
-* ``shard="tasks"``  the reference's partition, ``all_task_ids[rank::world_size]``
+* ``shard="tasks"`` (default) the reference's partition, ``all_task_ids[rank::world_size]``
   (src/eval.py:569-571): each rank runs whole tasks through ``predict_with_augmentations``,
   i.e. chunks of 16 left-padded prompts, the reference's exact candidate path.
-* ``shard="variants"`` (default) every (task x test x dihedral x permutation x sample) variant is
+* ``shard="variants"`` (opt-in, the fast path) every (task x test x dihedral x permutation x sample) variant is
   one sequence of one large batch: variants are dealt to ranks by length, prompts are built and
   candidates canonicalised on the device, one all-gather, every rank tallies.  Each rank then
   REPORTS only ``all_task_ids[rank::world_size]``, so a caller that sums the per-rank counters
   (src/eval.py:1203-1208) gets the same totals.  Prompts are not padded here, which is what the
   reference computes for the longest prompts of each of its chunks; for shorter rows the reference
-  reads the first token's logits at a padded index (src/inference.py:420-423) and can differ.
+  reads the first token's logits at a padded index (src/inference.py:420-423) and can differ; the
+  ``max_seq_len`` clamp is applied per wave of ``wave_size`` rows rather than per chunk of 16.
+  Because of those two differences it is not the default of the drop-in entry points.
+
+Seeded vote tie-breaks (``vote_seed``) use the task's position in ``sorted(challenges)`` on both
+paths, so a task votes the same way whichever path handled it.
 
 Test-time adaptation needs autograd through the model and stays on the reference module:
 ``tta_steps > 0`` raises ``NotImplementedError``.
@@ -124,11 +129,12 @@ def predict_all_variants(model, tasks: list[dict], device, example_ids: list[int
                          num_color_perms=8, top_k=2, max_output_tokens=900, num_samples=1,
                          sample_temperature=0.0, sample_top_k=None, constrain_decoding=False,
                          palette_penalty=2.0, shape_penalty=2.0, rank=0, world_size=1, vote_seed=None,
-                         group=None, wave_size: int = 1024):
+                         group=None, wave_size: int = 1024, vote_task_index: list[int] | None = None):
     """Votes and voting statistics of every (task, test input), computed cooperatively by all ranks.
 
     Returns ``(tops, stats)``: dicts keyed by ``(task_index, test_idx)``, identical on every rank when
     ``vote_seed`` is given (unseeded tie-breaks may order equal counts differently per rank).
+    ``vote_task_index[i]`` is the number that seeds task ``i``'s tie-break rng (default ``i``).
     """
     engine = _resolve_engine(model, device)
     table = fanout.TaskTable(tasks, engine.device, num_color_perms=num_color_perms,
@@ -151,7 +157,8 @@ def predict_all_variants(model, tasks: list[dict], device, example_ids: list[int
     tallies = fanout.tally_records(records, vt)
     tops, stats = {}, {}
     for key, (ranked_fn, n_total, n_valid) in tallies.items():
-        votes = ranked_fn(_vote_rng(vote_seed, *key) or random.Random())
+        seed_index = key[0] if vote_task_index is None else int(vote_task_index[key[0]])
+        votes = ranked_fn(_vote_rng(vote_seed, seed_index, key[1]) or random.Random())
         tops[key] = [g for g, _ in votes[:top_k]]
         counts = [c for _, c in ranked_fn(random.Random(0))]
         top = counts[0] if counts else 0
@@ -169,7 +176,9 @@ def _example_id(example_id_map, task_id) -> int:
 
 def _variant_votes(model, challenges, task_ids, device, example_id_map, rank, world_size, vote_seed, group,
                    wave_size, **gen):
-    """(tops, stats) per task id via the variant-sharded path; ids of tasks it cannot represent."""
+    """(tops, stats) per task id via the variant-sharded path; ids of tasks it cannot represent.
+    ``task_ids`` must be in the caller's canonical (sorted) order: a task's position in it seeds its
+    tie-break rng, the same number the per-task path uses."""
     good, bad = [], []
     for tid in task_ids:
         try:
@@ -183,7 +192,8 @@ def _variant_votes(model, challenges, task_ids, device, example_id_map, rank, wo
         tasks = [challenges[t] for t in good]
         tops, stats = predict_all_variants(model, tasks, device, [_example_id(example_id_map, t) for t in good],
                                            rank=rank, world_size=world_size, vote_seed=vote_seed, group=group,
-                                           wave_size=wave_size, **gen)
+                                           wave_size=wave_size,
+                                           vote_task_index=[task_ids.index(t) for t in good], **gen)
         for ti, tid in enumerate(good):
             n_tests = len(challenges[tid]["test"])
             out[tid] = ([tops[(ti, k)] for k in range(n_tests)], [stats[(ti, k)] for k in range(n_tests)])
@@ -197,7 +207,7 @@ def evaluate_dataset(model, challenges: dict, device, example_id_map: dict | Non
                      constrain_decoding: bool = False, palette_penalty: float = 2.0, shape_penalty: float = 2.0,
                      tta_steps: int = 0, tta_lr: float = 0.0, tta_weight_decay: float = 0.0,
                      tta_batch_tasks: int = 1, show_progress: bool = True, rank: int = 0, world_size: int = 1,
-                     *, shard: str = "variants", vote_seed: int | None = None, group=None,
+                     *, shard: str = "tasks", vote_seed: int | None = None, group=None,
                      wave_size: int = 1024) -> dict:
     """Same arguments, partition of REPORTED tasks and result dictionary as src/eval.py:512-702."""
     _no_tta(tta_steps)
@@ -252,7 +262,7 @@ def generate_submission(model, challenges: dict, output_path, device, example_id
                         sample_top_k: int | None = None, constrain_decoding: bool = False,
                         palette_penalty: float = 2.0, shape_penalty: float = 2.0, tta_steps: int = 0,
                         tta_lr: float = 0.0, tta_weight_decay: float = 0.0, tta_batch_tasks: int = 1,
-                        show_progress: bool = True, *, shard: str = "variants", vote_seed: int | None = None,
+                        show_progress: bool = True, *, shard: str = "tasks", vote_seed: int | None = None,
                         rank: int = 0, world_size: int = 1, group=None, wave_size: int = 1024) -> dict:
     """Write the submission file of src/eval.py:705-878: ``{task_id: [{"attempt_1": grid,
     "attempt_2": grid}, ...]}`` in the order of ``challenges``, ``[[0]]`` when nothing was voted, the
@@ -265,15 +275,16 @@ def generate_submission(model, challenges: dict, output_path, device, example_id
                sample_temperature=sample_temperature, sample_top_k=sample_top_k,
                constrain_decoding=constrain_decoding, palette_penalty=palette_penalty, shape_penalty=shape_penalty)
     task_ids = list(challenges.keys())
+    sorted_ids = sorted(task_ids)      # a task's position here seeds its tie-break rng, as in evaluate_dataset
     voted, bad = {}, task_ids
     if shard == "variants":
-        voted, bad = _variant_votes(model, challenges, task_ids, device, example_id_map, rank, world_size,
+        voted, bad = _variant_votes(model, challenges, sorted_ids, device, example_id_map, rank, world_size,
                                     vote_seed, group, wave_size, **gen)
     elif shard != "tasks":
         raise ValueError("shard must be 'variants' or 'tasks'")
     for task_id in bad:
         tr = evaluate_task(model, challenges[task_id], task_id, device, example_id_map=example_id_map,
-                           vote_seed=vote_seed, task_index=task_ids.index(task_id), **gen)
+                           vote_seed=vote_seed, task_index=sorted_ids.index(task_id), **gen)
         voted[task_id] = (tr["test_outputs"], tr["voting_stats"])
     submission = {}
     for task_id in task_ids:

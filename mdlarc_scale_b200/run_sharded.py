@@ -107,7 +107,7 @@ def main_evaluate(args, tasks, engine, rank, world, dev, dist):
     t0 = time.perf_counter()
     res = evaluation.evaluate_dataset(engine, challenges, dev, solutions=solutions, num_color_perms=args.perms,
                                       top_k=2, max_output_tokens=args.max_new, show_progress=False, rank=rank,
-                                      world_size=world, vote_seed=7, wave_size=args.wave)
+                                      world_size=world, vote_seed=7, wave_size=args.wave, shard="variants")
     torch.cuda.synchronize(dev)
     wall = time.perf_counter() - t0
     fields = ["correct_at_1", "correct_at_2", "total_test_examples", "my_tasks", "arc_tasks_scored"]

@@ -152,7 +152,7 @@ def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, eng
                              wave_size: int = 1024, stop_on_end: bool = True,
                              max_prefill_tokens: int = 65536, example_ids=None, constraints: dict | None = None,
                              temperature: float = 0.0, top_k: int = 0, sample_seed: int = 0,
-                             max_seq_len: int | None = None) -> np.ndarray:
+                             max_seq_len: int | None = None, gather: bool = True, timing: dict | None = None):
     """Generate this rank's variants and return every variant's candidate record in canonical
     variant order (uint8 ``[len(vt), RECORD_BYTES]``, identical on all ranks).
 
@@ -186,7 +186,7 @@ def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, eng
                     wave_cons[key] = np.ascontiguousarray(constraints[key][idx])
         sess = engine.new_session(n, int(lens.max()) + new, new, cap, stop_on_end=stop_on_end,
                                   out_tokens=tokens, constraints=wave_cons, temperature=temperature,
-                                  top_k=top_k, sample_seed=sample_seed + w0)
+                                  top_k=top_k, sample_seed=sample_seed, sample_stream=idx)
         ex = None
         if example_ids is not None:
             ex = torch.from_numpy(np.ascontiguousarray(np.asarray(example_ids)[idx], dtype=np.int32)).to(dev)
@@ -212,16 +212,35 @@ def generate_sharded_records(table, vt, max_new: int, rank: int, world: int, eng
         table.canonicalize(tokens, vt, idx, local[w0: w0 + n])   # straight into the gather slice
         sess.close()      # frees the wave's cache before the next wave allocates its own
         del sess, plans, tokens
-    return gather_records(rec, rank, world, vt.length, group)
+    if not gather:
+        return rec
+    return gather_records(rec, rank, world, vt.length, group, timing)
 
 
-def gather_records(rec: torch.Tensor, rank: int, world: int, lengths, group=None) -> np.ndarray:
+def gather_records(rec: torch.Tensor, rank: int, world: int, lengths, group=None,
+                   timing: dict | None = None) -> np.ndarray:
     """Complete the gather buffer ``rec`` (``[world * per, width]``, this rank's slice filled) with ONE
     in-place all-gather and return its rows in canonical variant order (host array)."""
     per = rec.shape[0] // world
     if world > 1:
         import torch.distributed as dist
+        timed = timing is not None and rec.is_cuda
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         dist.all_gather_into_tensor(rec, rec[rank * per: (rank + 1) * per], group=group)
+        if timed:
+            e1.record()
+            e1.synchronize()
+            timing["all_gather_ms"] = e0.elapsed_time(e1)
+    if timing is not None:
+        timing.setdefault("all_gather_ms", 0.0)
+        timing["gather_bytes"] = int(rec.numel() * rec.element_size())
+    return records_in_variant_order(rec, lengths, world)
+
+
+def records_in_variant_order(rec: torch.Tensor, lengths, world: int) -> np.ndarray:
+    """Rows of a complete gather buffer re-ordered to canonical variant order (host array)."""
     layout = gather_layout(lengths, world)
     valid = layout >= 0
     out = np.zeros((len(lengths),) + tuple(rec.shape[1:]), rec.cpu().numpy().dtype)

@@ -57,6 +57,41 @@ class B200TinyTransformer(torch.nn.Module):
         self.config = module.config
         self._device = torch.device(device)
 
+    def __getattr__(self, name):
+        # attributes of the wrapped module (num_parameters, token_embed, blocks, ...) read through
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(super().__getattr__("module"), name)
+
     def forward(self, input_ids, pos_xyz, example_ids=None, attention_mask=None, is_causal=True):
         eng = _resolve_engine(self.module, self._device)
         return forward_logits(eng, input_ids, pos_xyz, example_ids, attention_mask, is_causal)
+
+    def reset_cache(self) -> None:
+        """Nothing to reset: every call builds its own session (kept for callers of the reference API)."""
+
+    @torch.no_grad()
+    def generate(self, input_ids, pos_xyz, max_new_tokens, example_ids=None, temperature=1.0, top_k=None,
+                 greedy=True):
+        """The reference module's own ``generate`` (src/transformer.py:601-692), kept for its callers:
+        every new token takes the last position with x advanced by one modulo ``max_x`` (no grid-state
+        tracking, no END handling).  This is not the hot path (``generate_output`` is): each step
+        recomputes the logits of the whole prefix on the engine, which is exact for a causal model."""
+        ids, pos = input_ids, pos_xyz
+        for _ in range(int(max_new_tokens)):
+            logits = self.forward(ids, pos, example_ids)[:, -1, :]
+            if greedy:
+                nxt = logits.argmax(dim=-1, keepdim=True)
+            else:
+                probs = torch.softmax(logits / temperature, dim=-1)
+                if top_k is not None:
+                    v, _ = torch.topk(probs, min(top_k, probs.size(-1)))
+                    probs = torch.where(probs < v[:, [-1]], torch.zeros_like(probs), probs)
+                    probs = probs / probs.sum(dim=-1, keepdim=True)
+                nxt = torch.multinomial(probs, num_samples=1)
+            new_pos = pos[:, -1:, :].clone()
+            new_pos[:, :, 0] = (new_pos[:, :, 0] + 1) % int(self.config.max_x)
+            ids = torch.cat([ids, nxt.to(ids.dtype)], dim=1)
+            pos = torch.cat([pos, new_pos], dim=1)
+        return ids

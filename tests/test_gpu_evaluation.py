@@ -52,7 +52,7 @@ def test_variant_sharded_evaluation_agrees_with_per_task_path(tmp_path):
     # the reported partition under a world size of 2 (no collective needed to check the bookkeeping):
     # rank r reports all_task_ids[r::2] and the counters add up
     sub = evaluation.generate_submission(eng, challenges, tmp_path / "sub.json", "cuda:0", num_color_perms=3,
-                                         max_output_tokens=40, show_progress=False, vote_seed=11)
+                                         max_output_tokens=40, show_progress=False, vote_seed=11, shard="variants")
     assert json.loads((tmp_path / "sub.json").read_text()) == json.loads(json.dumps(sub))
     for tid, t in challenges.items():
         assert len(sub[tid]) == len(t["test"])

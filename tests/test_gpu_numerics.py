@@ -1,0 +1,133 @@
+"""Numeric edge cases of the CUDA path, through the C ABI:
+
+  * 3D RoPE in the QKV epilogue, checked directly on the K rows it writes to the cache (not only
+    through logits), including positions outside the tables, which must clamp like
+    RotaryEmbedding3D.apply_rotary (src/transformer.py:152-154);
+  * half-format range: weights that produce large activations must keep the logits within the
+    tolerance, and values that do not fit IEEE half must be counted (a warning), not faulted on.
+"""
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import have_b200
+from oracle import arc_model as om
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+
+
+def _tiny(seed=0, **kw):
+    cfg = om.make_config("tiny", max_seq_len=4096)
+    return cfg, om.round_bf16(om.perturb_state(om.init_state(cfg, seed=seed, **kw), seed=seed + 1))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def _need_gpu():
+    if not have_b200():
+        pytest.fail("these tests need a B200 (compute capability 10.x)")
+
+
+@pytest.mark.parametrize("gemm_path", ["simt", "auto"])
+def test_rope_epilogue_writes_rotated_keys_and_clamps_positions(gemm_path):
+    """Layer-0 K rows in the cache = RoPE(W_k rmsnorm(embed)) at the clamped position, for in-range
+    and out-of-range (x, y, z); rows that clamp to the same position are bitwise identical."""
+    from mdlarc_scale_b200.engine import Engine, plan_prefill
+    cfg, sd = _tiny()
+    eng = Engine(sd, cfg, "cuda:0", gemm_path=gemm_path)
+    # 48 rows so that the tensor-core GEMM runs when gemm_path is "auto" (M > 32)
+    base = [(99, 99, 99), (31, 31, 7), (-1, 0, 9), (0, 0, 7), (5, 7, 3), (30, 29, 1), (0, 0, 0), (17, 2, 4)]
+    pos = np.array([base[i % len(base)] for i in range(48)], dtype=np.int64)[None]
+    ids = np.full((1, 48), 3, dtype=np.int64)       # one token everywhere: rows differ by position only
+    ids[0, 40:] = np.arange(8)                      # and a few other tokens
+    mask = np.ones((1, 48), dtype=bool)
+    sess = eng.new_session(1, 64, 1, 64, stop_on_end=False)
+    sess.prefill(plan_prefill(ids, pos, mask, np.arange(1)).to(torch.device("cuda:0")), None)
+    sess.poll()
+    H, hd, L = cfg.n_heads, 64, cfg.n_layers
+    cache = sess.kv_cache.view(torch.bfloat16).view(L, 2, 1, H, 64, hd)
+    k_gpu = cache[0, 0, 0, :, :48].float().cpu()                       # [H, 48, 64]
+    v_gpu = cache[0, 1, 0, :, :48].float().cpu()
+    # oracle: the same arithmetic in fp32 with the reference's clamp
+    ids_t, pos_t = torch.from_numpy(ids), torch.from_numpy(pos)
+    x = sd["token_embed.weight"][ids_t]
+    h = om.rmsnorm(x, sd["blocks.0.ln1.weight"], cfg.norm_eps)
+    q, k, v = torch.nn.functional.linear(h, sd["blocks.0.attn.qkv_proj.weight"]).reshape(1, 48, 3, H, hd).unbind(2)
+    _, k_rot = om.apply_rope(cfg, om.rope_tables(cfg), q, k, pos_t)
+    k_ref = k_rot[0].transpose(0, 1)                                   # [H, 48, 64]
+    v_ref = v[0].transpose(0, 1)
+    scale = k_ref.abs().max().item()
+    e_k = (k_gpu - k_ref).abs().max().item()
+    e_v = (v_gpu - v_ref).abs().max().item()
+    print(f"rope epilogue ({gemm_path}): max |K| {scale:.3f}, K error {e_k:.5f}, V error {e_v:.5f}")
+    assert e_k < 0.012 * scale and e_v < 0.012 * scale                 # bf16 cache rows: 2^-8 relative + operand rounding
+    # an unrotated K must NOT pass (the check has teeth)
+    assert (k_gpu - k[0].transpose(0, 1)).abs().max().item() > 0.05 * scale
+    # clamping: (99, 99, 99) == (31, 31, 7) and (-1, 0, 9) == (0, 0, 7) for the same token
+    assert torch.equal(cache[0, 0, 0, :, 0], cache[0, 0, 0, :, 1])
+    assert torch.equal(cache[0, 0, 0, :, 2], cache[0, 0, 0, :, 3])
+    assert not torch.equal(cache[0, 0, 0, :, 0], cache[0, 0, 0, :, 2])
+    sess.close()
+    eng.close()
+
+
+def _forward_error(sd, cfg, seed=71):
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import pad_prompts
+    from mdlarc_scale_b200.transformer import forward_logits
+    eng = Engine(sd, cfg, "cuda:0")
+    tasks = synthetic.capped_tasks(seed, 4, 2, 3, 6, 12, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
+    ex = torch.arange(len(prompts))
+    got = forward_logits(eng, ids_t, pos_t, ex, mask_t).cpu()
+    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
+    err = (got[mask_t] - want[mask_t]).abs()
+    sat = eng.saturation_count()
+    eng.close()
+    return err.max().item(), err.mean().item(), want[mask_t].abs().max().item(), sat, int(mask.sum())
+
+
+def test_large_activations_stay_within_tolerance():
+    """Seeded weights with the attention projection scaled by 8 (scores 64 times larger: a sharply
+    peaked softmax, |q.k| in the hundreds) and one up-projection row scaled by 64 (an outlier
+    channel), the same weights on both sides.  Nothing saturates and the logits stay in tolerance."""
+    cfg, sd = _tiny(seed=2, embed_gain=8.0)
+    sd = dict(sd)
+    for l in range(cfg.n_layers):
+        sd[f"blocks.{l}.attn.qkv_proj.weight"] = sd[f"blocks.{l}.attn.qkv_proj.weight"] * 8.0
+        w = sd[f"blocks.{l}.ffn.fc_up.weight"].clone()
+        w[3 + l] *= 64.0
+        sd[f"blocks.{l}.ffn.fc_up.weight"] = w
+    sd = om.round_bf16(sd)
+    e_max, e_mean, scale, sat, n = _forward_error(sd, cfg)
+    print(f"large activations: {n} tokens, max |logit| {scale:.2f}, max abs error {e_max:.5f}, mean {e_mean:.6f}, "
+          f"saturations {sat}")
+    assert sat == 0
+    assert e_max < TOL
+
+
+def test_half_saturation_is_counted_not_fatal():
+    """An up projection scaled by 3e5 pushes the SwiGLU activations past 65504: they are clamped, the
+    engine counts them, no device error is raised, and the count resets."""
+    cfg, sd = _tiny(seed=3)
+    sd = dict(sd)
+    sd["blocks.1.ffn.fc_up.weight"] = sd["blocks.1.ffn.fc_up.weight"] * 3.0e5
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    eng = Engine(sd, cfg, "cuda:0")
+    assert eng.saturation_count() == 0
+    tasks = synthetic.capped_tasks(5, 40, 1, 2, 2, 6, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    tr = generate_tokens(eng, ids, pos, mask, None, 4, stop_on_end=False)     # poll() inside raises on a device error
+    toks = tr.tokens.cpu()
+    assert toks.min() >= 0 and toks.max() <= 13
+    n = eng.saturation_count()
+    assert n > 0
+    assert eng.saturation_count() == 0                                          # cleared by the read
+    print(f"half saturation: {n} clamped pairs counted, generation completed")
+    eng.close()

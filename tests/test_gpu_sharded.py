@@ -48,3 +48,54 @@ def test_sharded_world1_matches_direct_generation_and_oracle_vote():
         want = arc_vote.aaivr_predict(preds, 2, tasks[ti]["test"][te]["input"],
                                       rng=random.Random(7 + 1000003 * ti + te))
         assert votes[(ti, te)] == want
+
+
+def test_sampling_streams_are_per_variant_and_independent_of_world_size():
+    """Self-consistency sampling under variant sharding: the random stream of a sequence is keyed on
+    its job-wide variant number, not on the rank-local cache row.  (a) The four samples of one
+    prompt differ from each other although the round-robin deal puts them at the same local row of
+    consecutive ranks; (b) rank 0 of 2 and rank 1 of 2, run back to back on this GPU and merged as
+    the all-gather would, give the records of the single-rank run; (c) the device's draw equals the
+    host mirror of the counter-based generator applied to the same logits."""
+    if not have_b200():
+        pytest.fail("this test needs a B200 (compute capability 10.x)")
+    from mdlarc_scale_b200 import fanout, sharding, synthetic
+    from mdlarc_scale_b200.engine import Engine, sample_uniform
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    cfg, sd = synthetic.seeded_weights("tiny", 0, 8.0)
+    eng = Engine(sd, cfg, "cuda:0")
+    tasks = synthetic.capped_tasks(9, 2, 1, 2, 2, 5, None)
+    table = fanout.TaskTable(tasks, eng.device, num_color_perms=2)
+    vt = table.variants(num_samples=4)                 # 2 tasks x 8 x 2 x 4 samples = 128 variants
+    kw = dict(temperature=1.0, top_k=0, sample_seed=1234, wave_size=64)
+    one = sharding.generate_sharded_records(table, vt, 24, 0, 1, eng, **kw)
+    parts = [sharding.generate_sharded_records(table, vt, 24, r, 2, eng, gather=False, **kw) for r in range(2)]
+    per = sharding.rows_per_rank(len(vt), 2)
+    merged = parts[0].clone()
+    merged[per:] = parts[1][per:]
+    two = sharding.records_in_variant_order(merged, vt.length, 2)
+    same = int((one == two).all(axis=1).sum())
+    assert same >= int(0.95 * len(vt)), f"only {same} of {len(vt)} records agree between world sizes 1 and 2"
+    # (a) the samples of one prompt: variants 4 k .. 4 k + 3
+    distinct = 0
+    for k in range(len(vt) // 4):
+        rows = {one[4 * k + s].tobytes() for s in range(4)}
+        distinct += len(rows) > 1
+    assert distinct >= int(0.9 * (len(vt) // 4)), distinct
+    # (c) first sampled token of a few rows against the host mirror, with explicit stream ids
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts * 8, positions * 8, left=False)
+    streams = np.arange(1000, 1000 + ids.shape[0])
+    sess = eng.new_session(ids.shape[0], ids.shape[1] + 2, 2, 4096, stop_on_end=False, temperature=0.8,
+                           sample_seed=77, sample_stream=streams)
+    tr = generate_tokens(eng, ids, pos, mask, None, 2, stop_on_end=False, want_logits=True, session=sess)
+    logits = tr.first_logits.double().cpu().numpy()
+    first = tr.tokens[:, 0].cpu().numpy()
+    hits = 0
+    for b in range(ids.shape[0]):
+        p = np.exp((logits[b] - logits[b].max()) / 0.8)
+        u = sample_uniform(77, int(streams[b]), 0) * p.sum()
+        hits += int(np.searchsorted(np.cumsum(p), u, side="right")) == int(first[b])
+    assert hits >= ids.shape[0] - 1, (hits, ids.shape[0])   # fp32 vs fp64 CDF edges may move one draw
+    assert len(set(first.tolist())) > 1
+    eng.close()

@@ -103,3 +103,19 @@ def test_two_gloo_ranks_equal_single_process(tmp_path):
         assert cands == want_c
         assert votes == want_v
         assert votes_rec == want_v
+
+
+def test_sampling_counter_streams_are_distinct_and_deal_never_shares_one():
+    """The counter-based uniform number depends on (seed, stream id, position); stream ids are the
+    job-wide variant numbers, so the length-sorted round-robin deal can never give two variants
+    the same stream, whatever the number of ranks."""
+    from mdlarc_scale_b200.engine import sample_uniform
+    u = [sample_uniform(5, s, i) for s in range(64) for i in range(8)]
+    assert all(0.0 <= x < 1.0 for x in u) and len(set(u)) == len(u)
+    assert sample_uniform(5, 3, 2) == sample_uniform(5, 3, 2) != sample_uniform(6, 3, 2)
+    assert abs(float(np.mean([sample_uniform(1, s, 0) for s in range(4096)])) - 0.5) < 0.02
+    lengths = np.repeat(np.array([30, 30, 41, 17]), 4)          # 4 samples per prompt: equal lengths
+    for world in (1, 2, 3, 4, 8):
+        dealt = sharding.assign(lengths, world)
+        ids = np.concatenate(dealt)
+        assert sorted(ids.tolist()) == list(range(len(lengths)))      # each variant (= stream id) exactly once
