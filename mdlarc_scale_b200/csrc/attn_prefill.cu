@@ -29,6 +29,7 @@
 #include <cstdlib>
 
 #include "attn_prefill.cuh"
+#include "launch.cuh"
 #include "gemm.cuh"
 #include "ptx_sm100.cuh"
 
@@ -155,6 +156,8 @@ __global__ void __maxnreg__(200)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, AttnPrefillArgs a, uint32_t idesc_qk,
                     uint32_t idesc_pv) {
+  pdl_launch_dependents();
+  pdl_wait();   // the prologue below already reads the work list from global memory
   extern __shared__ uint8_t smem_raw[];
   __shared__ int s_max_cnt[8];
   const uint32_t raw = smem_u32(smem_raw);
@@ -598,8 +601,9 @@ int arcb_launch_attn_prefill(const AttnPrefillArgs& a, cudaStream_t stream) {
   const uint32_t idesc_qk = umma_idesc_f16(BQ, BKV, fmt, fmt, 0, 0);
   const uint32_t idesc_pv = umma_idesc_f16(BQ, HD, fmt, fmt, 0, 1);  // B = V is MN-major
   dim3 grid(a.n_qblocks, a.n_heads);
+  cudaError_t le = cudaSuccess;
 #define ARCB_LAUNCH_FLASH(SM, PL) \
-  attn_prefill_kernel<SM, PL><<<grid, N_THREADS, SMEM_BYTES, stream>>>(tq, tk, tv, a, idesc_qk, idesc_pv)
+  le = arcb_launch(attn_prefill_kernel<SM, PL>, grid, dim3(N_THREADS), SMEM_BYTES, stream, tq, tk, tv, a, idesc_qk, idesc_pv)
   if (!a.act_f16) {
     ARCB_LAUNCH_FLASH(0, 0);
   } else {
@@ -613,5 +617,5 @@ int arcb_launch_attn_prefill(const AttnPrefillArgs& a, cudaStream_t stream) {
   }
 #undef ARCB_LAUNCH_FLASH
   arcb_count_launch(1);
-  return (int)cudaGetLastError();
+  return (int)le;
 }

@@ -9,6 +9,7 @@
 // With n_splits > 1 every split writes (m, l, acc[64]) to scratch and a second kernel merges
 // the splits; with n_splits == 1 the normalised output is written directly.
 #include "attn_stream.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -42,6 +43,8 @@ __device__ __forceinline__ void axpy8(float (&acc)[8], float p, const uint4& v) 
 
 __global__ void __launch_bounds__(WARPS_PER_CTA * 32)
 attn_stream_kernel(AttnStreamArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * WARPS_PER_CTA + (threadIdx.x >> 5);
   const long long n_work = (long long)a.n_items * a.n_heads * a.n_splits;
@@ -177,6 +180,8 @@ attn_stream_kernel(AttnStreamArgs a) {
 // One warp per (item, head): lane d handles dims 2d, 2d+1.
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(AttnStreamArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long ih = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (ih >= (long long)a.n_items * a.n_heads) return;
@@ -206,12 +211,12 @@ int arcb_launch_attn_stream(const AttnStreamArgs& a, cudaStream_t stream) {
   const long long n_work = (long long)a.n_items * a.n_heads * a.n_splits;
   const long long blocks = (n_work + WARPS_PER_CTA - 1) / WARPS_PER_CTA;
   if (blocks > 0x7fffffffLL) return -1;
-  attn_stream_kernel<<<(unsigned)blocks, WARPS_PER_CTA * 32, 0, stream>>>(a);
+  cudaError_t e = arcb_launch(attn_stream_kernel, dim3((unsigned)blocks), dim3(WARPS_PER_CTA * 32), 0, stream, a);
   arcb_count_launch(1);
-  if (a.n_splits > 1) {
+  if (e == cudaSuccess && a.n_splits > 1) {
     const long long nb = ((long long)a.n_items * a.n_heads + 3) / 4;
-    attn_combine_kernel<<<(unsigned)nb, 128, 0, stream>>>(a);
+    e = arcb_launch(attn_combine_kernel, dim3((unsigned)nb), dim3(128), 0, stream, a);
     arcb_count_launch(1);
   }
-  return (int)cudaGetLastError();
+  return (int)e;
 }

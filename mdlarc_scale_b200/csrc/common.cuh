@@ -33,6 +33,11 @@ __device__ __forceinline__ void arcb_count_saturation(int* err) {
   if (err) atomicAdd(err + 1, 1);
 }
 
+// ---- programmatic dependent launch (see launch.cuh for the protocol) ----
+// Both are no-ops for a kernel that was launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ---- 16-bit activation formats -------------------------------------------
 // act_f16 != 0: IEEE half (values clamped to the finite half range), else bfloat16.
 

@@ -2,6 +2,7 @@
 // state + the decode-step CUDA graph) and the standalone operator entry points.
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -11,6 +12,7 @@
 #include "attn_prefill.cuh"
 #include "attn_stream.cuh"
 #include "gemm.cuh"
+#include "launch.cuh"
 #include "rowops.cuh"
 
 // ---------------------------------------------------------------------------
@@ -20,6 +22,23 @@ static thread_local std::string g_last_error;
 static std::atomic<long long> g_launches{0};
 
 void arcb_count_launch(long long n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// Programmatic dependent launch: on unless ARCB_PDL=0 (read once); switched off for the process if a
+// graph capture with programmatic edges is refused.
+static std::atomic<int> g_pdl{-1};
+bool arcb_pdl_enabled() {
+  int v = g_pdl.load(std::memory_order_relaxed);
+  if (v < 0) {
+    const char* e = getenv("ARCB_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+    g_pdl.store(v, std::memory_order_relaxed);
+  }
+  return v != 0;
+}
+void arcb_pdl_set(bool on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
+static thread_local bool g_pdl_suppress = false;
+void arcb_pdl_suppress(bool on) { g_pdl_suppress = on; }
+bool arcb_pdl_suppressed() { return g_pdl_suppress; }
 
 void arcb_set_last_error(const char* msg) { g_last_error = msg ? msg : ""; }
 
@@ -380,6 +399,15 @@ static bool use_tc_for(const arcb_engine* e, int M, int N, int K) {
   return M > 32;
 }
 
+// Suppresses the programmatic-launch attribute for this thread's launches while on (and on scope exit
+// restores the default, whichever way the function returns).
+struct PdlSuppressGuard {
+  bool active = false;
+  void on() { arcb_pdl_suppress(true); active = true; }
+  void off() { if (active) { arcb_pdl_suppress(false); active = false; } }
+  ~PdlSuppressGuard() { off(); }
+};
+
 // One transformer block over `rows` rows of the residual stream s->x (xn16 already holds
 // ln1(x)); on return xn16 holds the next block's ln1(x) (or is stale after the last block).
 static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int* slot, const int* seq,
@@ -410,6 +438,7 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
   CKL(arcb_launch_gemm(s->xn16, L.w_qkv, ep, d, f16, use_tc_for(e, rows, 3 * d, d), stream), "qkv gemm");
 
   // attention
+  PdlSuppressGuard plain_edges;
   const bool flash = prefill && c.attn_path == ARCB_ATTN_AUTO && pa && pa->n_qblocks > 0 && pa->d_kv_row &&
                      pa->d_qblock_kv0 && pa->n_kv_rows > 0 && arcb_attn_prefill_available();
   if (flash) {
@@ -429,7 +458,11 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
     const bool probe = !prefill && l == 0 && s->probe_begin && s->probe_end;
     // cudaEventRecordExternal: under stream capture this becomes an event-record NODE of the graph (a
     // plain record would only mark a capture dependency and leave the event unusable for timing)
-    if (probe) CK(cudaEventRecordWithFlags(s->probe_begin, stream, cudaEventRecordExternal));
+    // the kernels next to the two event-record nodes are joined to them by ordinary edges
+    if (probe) {
+      plain_edges.on();
+      CK(cudaEventRecordWithFlags(s->probe_begin, stream, cudaEventRecordExternal));
+    }
     CKL(arcb_launch_attn_stream(aa, stream), "attention");
     if (probe) { CK(cudaEventRecordWithFlags(s->probe_end, stream, cudaEventRecordExternal)); s->probe_recorded = true; }
   }
@@ -438,6 +471,7 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
   GemmEpilogue er{};
   er.mode = EPI_RESID; er.M = rows; er.N = d; er.x = s->x; er.bias = nullptr; er.act_f16 = f16; er.err = e->d_err;
   CKL(arcb_launch_gemm(s->attn16, L.w_out, er, d, f16, use_tc_for(e, rows, d, d), stream), "out_proj gemm");
+  plain_edges.off();
   CKL(arcb_launch_rmsnorm(s->x, L.ln2_w, s->xn16, rows, d, c.norm_eps, f16, stream), "ln2");
   // gate | up + SwiGLU
   GemmEpilogue eg{};
@@ -533,7 +567,7 @@ extern "C" int arcb_decode(arcb_session* s, int32_t n_steps, void* stream_v) {
   if (!s->armed) return fail(ARCB_E_STATE, "arcb_prefill with first-token rows must run before arcb_decode");
   if (n_steps <= 0) return ARCB_OK;
   cudaStream_t stream = (cudaStream_t)stream_v;
-  if (!s->graph_exec) {
+  for (int attempt = 0; !s->graph_exec && attempt < 2; ++attempt) {
     const long long before = g_launches.load();
     CK(cudaStreamBeginCapture(s->capture_stream, cudaStreamCaptureModeThreadLocal));
     int r = record_decode_step(s, s->capture_stream);
@@ -541,10 +575,21 @@ extern "C" int arcb_decode(arcb_session* s, int32_t n_steps, void* stream_v) {
     cudaError_t ce = cudaStreamEndCapture(s->capture_stream, &g);
     s->graph_kernels = g_launches.load() - before;
     g_launches.fetch_sub(s->graph_kernels);  // recording is not launching
-    if (r) { if (g) cudaGraphDestroy(g); return r; }
-    if (ce != cudaSuccess) return fail_cuda(ce, "cudaStreamEndCapture");
-    s->graph = g;
-    CK(cudaGraphInstantiate(&s->graph_exec, s->graph, 0));
+    cudaGraphExec_t ge = nullptr;
+    if (r == 0 && ce == cudaSuccess) ce = cudaGraphInstantiate(&ge, g, 0);
+    if (r == 0 && ce == cudaSuccess) {
+      s->graph = g;
+      s->graph_exec = ge;
+      break;
+    }
+    if (g) cudaGraphDestroy(g);
+    cudaGetLastError();
+    if (attempt == 0 && arcb_pdl_enabled()) {
+      arcb_pdl_set(false);   // capture with programmatic edges refused: record plain launches instead
+      continue;
+    }
+    if (r) return r;
+    return fail_cuda(ce, "capture / instantiate of the decode step");
   }
   for (int i = 0; i < n_steps; ++i) CK(cudaGraphLaunch(s->graph_exec, stream));
   arcb_count_launch(s->graph_kernels * n_steps);

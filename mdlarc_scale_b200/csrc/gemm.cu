@@ -8,6 +8,7 @@
 //   gemm_simt_kernel : CUDA-core tile kernel for skinny M (weight streaming) and as
 //                      the cross-check of the tensor-core path.
 #include "gemm.cuh"
+#include "launch.cuh"
 #include "ptx_sm100.cuh"
 
 using namespace sm100;
@@ -287,6 +288,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                const __grid_constant__ CUtensorMap tmap_z, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
                int tiles_total) {
   using Cfg = TcCfg<BN>;
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -327,6 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // everything above touched only shared / tensor memory and the kernel's own parameters
 
   if (warp == 0) {
     // ---- TMA producer ----
@@ -472,6 +475,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
                 int tiles_total) {
   using Cfg = Tc2Cfg;
   constexpr int BN = Cfg::BN;
+  pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -514,6 +518,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrive / TMA completion
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();   // everything above touched only shared / tensor memory and the kernel's own parameters
 
   if (warp == 0) {
     // ---- TMA producer (both CTAs) ----
@@ -639,6 +644,8 @@ template <int MODE>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const uint16_t* __restrict__ A, const uint16_t* __restrict__ W, GemmEpilogue ep,
                  int K, int a_f16) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float As[SM_BK][SM_BM + 1];
   __shared__ __align__(16) float Ws[SM_BK][SM_BN + 4];
   const int tid = threadIdx.x;
@@ -830,26 +837,27 @@ int arcb_gemm_init() {
 }
 
 template <int BN, int MODE>
-static void launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
+static cudaError_t launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
                       const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + BN - 1) / BN, tiles_m = (ep.M + TC_BM - 1) / TC_BM;
   const int tiles = tiles_n * tiles_m;
   const int sms = num_sms();
   const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
-  gemm_tc_kernel<BN, MODE><<<tiles < sms ? tiles : sms, TC_THREADS, TcCfg<BN>::SMEM_BYTES + epi_stage_bytes<MODE>(),
-                             stream>>>(ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
+  return arcb_launch(gemm_tc_kernel<BN, MODE>, dim3(tiles < sms ? tiles : sms), dim3(TC_THREADS),
+                     TcCfg<BN>::SMEM_BYTES + epi_stage_bytes<MODE>(), stream, ta, tb, tx, ty, tz, ep, K, idesc, tiles_n,
+                     tiles);
 }
 
 template <int MODE>
-static void launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
+static cudaError_t launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
                        const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + 255) / 256, tiles_m = (ep.M + 255) / 256;
   const int tiles = tiles_n * tiles_m;
   const int mp = max_pairs();
   const int pairs = tiles < mp ? tiles : mp;
   const uint32_t idesc = umma_idesc_f16(256, 256, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
-  gemm_tc2_kernel<MODE><<<2 * pairs, TC_THREADS, Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>(), stream>>>(
-      ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
+  return arcb_launch(gemm_tc2_kernel<MODE>, dim3(2 * pairs), dim3(TC_THREADS),
+                     Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>(), stream, ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
 }
 
 int arcb_gemm_max_pairs() { return max_pairs(); }
@@ -895,17 +903,19 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
         if (r) return 1000 + r;
       }
     }
-    if (pair) launch_tc2<MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
-    else if (wide) launch_tc<256, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
-    else launch_tc<128, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
-  } else {
-    dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
-    gemm_simt_kernel<MODE><<<grid, 256, 0, stream>>>(reinterpret_cast<const uint16_t*>(a16),
-                                                     reinterpret_cast<const uint16_t*>(w16), ep, K,
-                                                     act_f16);
+    cudaError_t le;
+    if (pair) le = launch_tc2<MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
+    else if (wide) le = launch_tc<256, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
+    else le = launch_tc<128, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
+    arcb_count_launch(1);
+    return (int)le;
   }
+  dim3 grid(N / SM_BN, (M + SM_BM - 1) / SM_BM);
+  const cudaError_t le = arcb_launch(gemm_simt_kernel<MODE>, grid, dim3(256), 0, stream,
+                                     reinterpret_cast<const uint16_t*>(a16), reinterpret_cast<const uint16_t*>(w16), ep,
+                                     K, act_f16);
   arcb_count_launch(1);
-  return (int)cudaGetLastError();
+  return (int)le;
 }
 
 int arcb_launch_gemm(const void* a16, const void* w16, const GemmEpilogue& ep, int K, int act_f16,

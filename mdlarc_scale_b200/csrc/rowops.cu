@@ -5,6 +5,7 @@
 //   head          : final RMSNorm -> 14 logits -> argmax (+ greedy-loop bookkeeping)
 //   pack_rows     : fp32 -> bf16-rounded weights in kernel layout
 #include "rowops.cuh"
+#include "launch.cuh"
 
 namespace {
 
@@ -52,6 +53,8 @@ __device__ __forceinline__ void row_embed(float* __restrict__ x, const float* __
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
 rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint16_t* __restrict__ out,
                int rows, int d, float eps, int act_f16) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
   if (row >= rows) return;
   row_norm_store(x + (size_t)row * d, w, out + (size_t)row * d, d, eps, act_f16, threadIdx.x & 31);
@@ -59,6 +62,8 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint16_
 
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
 embed_norm_kernel(EmbedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
   if (row >= a.rows) return;
   const int lane = threadIdx.x & 31;
@@ -79,6 +84,8 @@ embed_norm_kernel(EmbedArgs a) {
 // embedding of the fed token and the first RMSNorm of the step.
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
 decode_begin_kernel(DecodeState st, EmbedArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
   if (b >= st.n_seqs) return;
   const int lane = threadIdx.x & 31;
@@ -128,6 +135,8 @@ decode_begin_kernel(DecodeState st, EmbedArgs a) {
 
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
 head_kernel(HeadArgs a, DecodeState st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int i = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
   if (i >= a.rows) return;
   const int lane = threadIdx.x & 31;
@@ -297,30 +306,33 @@ int arcb_launch_rmsnorm(const float* x, const float* w, void* out16, int rows, i
                         int act_f16, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (d % 4) return -1;
-  rmsnorm_kernel<<<(rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA, ROWS_PER_CTA * 32, 0, stream>>>(
-      x, w, reinterpret_cast<uint16_t*>(out16), rows, d, eps, act_f16);
+  const cudaError_t e = arcb_launch(rmsnorm_kernel, dim3((rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA), dim3(ROWS_PER_CTA * 32), 0,
+                                    stream, x, w, reinterpret_cast<uint16_t*>(out16), rows, d, eps, act_f16);
   arcb_count_launch(1);
-  return (int)cudaGetLastError();
+  return (int)e;
 }
 
 int arcb_launch_embed_norm(const EmbedArgs& a, cudaStream_t stream) {
   if (a.rows <= 0) return 0;
-  embed_norm_kernel<<<(a.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA, ROWS_PER_CTA * 32, 0, stream>>>(a);
+  const cudaError_t e = arcb_launch(embed_norm_kernel, dim3((a.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA),
+                                    dim3(ROWS_PER_CTA * 32), 0, stream, a);
   arcb_count_launch(1);
-  return (int)cudaGetLastError();
+  return (int)e;
 }
 
 int arcb_launch_decode_begin(const DecodeState& st, const EmbedArgs& a, cudaStream_t stream) {
-  decode_begin_kernel<<<(st.n_seqs + ROWS_PER_CTA - 1) / ROWS_PER_CTA, ROWS_PER_CTA * 32, 0, stream>>>(st, a);
+  const cudaError_t e = arcb_launch(decode_begin_kernel, dim3((st.n_seqs + ROWS_PER_CTA - 1) / ROWS_PER_CTA),
+                                    dim3(ROWS_PER_CTA * 32), 0, stream, st, a);
   arcb_count_launch(1);
-  return (int)cudaGetLastError();
+  return (int)e;
 }
 
 int arcb_launch_head(const HeadArgs& a, const DecodeState& st, cudaStream_t stream) {
   if (a.rows <= 0) return 0;
-  head_kernel<<<(a.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA, ROWS_PER_CTA * 32, 0, stream>>>(a, st);
+  const cudaError_t e = arcb_launch(head_kernel, dim3((a.rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA), dim3(ROWS_PER_CTA * 32),
+                                    0, stream, a, st);
   arcb_count_launch(1);
-  return (int)cudaGetLastError();
+  return (int)e;
 }
 
 int arcb_launch_pack_rows(const float* src, void* dst, long long rows, long long cols, int blk,

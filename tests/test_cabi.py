@@ -36,7 +36,7 @@ def test_struct_sizes_match_c_layout():
     import ctypes as C
     from mdlarc_scale_b200 import _lib
     assert C.sizeof(_lib.Config) == 14 * 4
-    assert C.sizeof(_lib.SessionDesc) == 128  # sizeof(arcb_session_desc) printed by a C compile of the header
+    assert C.sizeof(_lib.SessionDesc) == 136  # sizeof(arcb_session_desc) printed by a C compile of the header
     assert C.sizeof(_lib.PrefillArgs) == 176
     assert C.sizeof(_lib.PromptBuildArgs) == 160
     assert C.sizeof(_lib.CandidateArgs) == 96
