@@ -427,6 +427,43 @@ def profile_fanout(args):
                                        "gbs": canon_bytes / canon_ms / 1e6}}))
 
 
+def torch_gpu_baseline_sample(dev, batch: int):
+    """The reference's own generate_output (PyTorch eager: cuBLAS linears, SDPA attention, its Python
+    decode loop) on THIS GPU in bf16, on one full step of the same workload (same generator, same
+    sequences per step, same token budget, END suppressed).  A library-call baseline: what the
+    hand-written kernels and the graph-captured step have to beat on equal hardware.  Returns None when
+    the reference files are not present."""
+    ref = _reference_model()
+    if ref is None:
+        return None
+    model, generate_output = ref
+    ids, pos, mask = make_batch(424242, batch)
+    try:
+        gpu_model = model.to(device=dev, dtype=torch.bfloat16)
+        ids_t, pos_t, mask_t = (torch.from_numpy(a).to(dev) for a in (ids, pos, mask))
+        with torch.no_grad():
+            generate_output(gpu_model, ids_t[:8], pos_t[:8], None, mask_t[:8], max_new_tokens=4, stop_on_end=False)
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = generate_output(gpu_model, ids_t, pos_t, None, mask_t, max_new_tokens=MAX_NEW, stop_on_end=False)
+            e1.record()
+            e1.synchronize()
+        dt = e0.elapsed_time(e1) / 1e3
+        gen = out.shape[1] - ids.shape[1]
+        res = {"value": batch * gen / dt, "unit": "tokens/s", "seconds": dt, "sequences": batch, "new_tokens": gen,
+               "dtype": "bf16", "same_config": True,
+               "what": "reference generate_output (src/inference.py), unmodified, PyTorch eager on this GPU, "
+                       "inputs resident on the device, CUDA-event timed"}
+        del out, ids_t, pos_t, mask_t
+    except Exception as exc:  # e.g. out of memory for its zero-filled padded cache
+        res = {"value": None, "error": f"{type(exc).__name__}: {str(exc)[:160]}"}
+    finally:
+        model.to(device="cpu", dtype=torch.float32)
+        torch.cuda.empty_cache()
+    return res
+
+
 def prefill_heavy_sample(engine, dev, repeats: int = 3):
     """One prefill call of the prefill-heavy large configuration: 6 prompts of 5 pairs of 30x30 grids
     plus a 30x30 test input (10 247 tokens each, 61 482 packed tokens), timed with CUDA events.
@@ -638,6 +675,10 @@ def run_ours(args, rank, world, local_rank):
         engine.close()
         torch.cuda.empty_cache()
         extras["vote_pipeline"] = vote_pipeline_sample(rank, world, dev, dist)
+        if rank == 0 and world == 1 and not args.no_torch_gpu:
+            tg = torch_gpu_baseline_sample(dev, B)
+            if tg is not None:
+                extras["torch_gpu_baseline"] = tg
     gen_tokens = world * args.steps * B * MAX_NEW
     clocks = sampler.summary()
     if rank == 0:
@@ -691,6 +732,8 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=112)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end leg (profiling runs)")
+    ap.add_argument("--no-torch-gpu", action="store_true",
+                    help="skip the reference's own PyTorch path timed on this GPU (N = 1 only)")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the prefill-heavy prefill call and the sharded vote pipeline sample")
     ap.add_argument("--profile-attn", type=int, default=0, metavar="T",

@@ -129,7 +129,11 @@ typedef struct arcb_session_desc {
   int32_t max_new;            /* generated-token budget per sequence                  */
   int32_t max_prefill_tokens; /* largest packed-token count of one arcb_prefill call  */
   int32_t attn_splits;        /* split-K factor of decode attention; 0 = choose       */
-  int32_t stop_on_end;        /* 1: a row that emits END is frozen (emits END after)  */
+  int32_t stop_on_end;        /* 0: END is an ordinary token; 1: a row that emits END is
+                                 counted as finished and frozen (emits END afterwards, its
+                                 attention is skipped); 2: counted as finished but decoded on,
+                                 as the reference does until every row of its batch has
+                                 finished (src/inference.py:593-626)                      */
   void* d_kv_cache;           /* bf16 [L][2][B][H][t_max][64]                         */
   int64_t kv_cache_bytes;
   void* d_workspace;          /* >= arcb_session_workspace_bytes(...)                 */

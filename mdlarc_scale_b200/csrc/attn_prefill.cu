@@ -149,10 +149,11 @@ struct Bars {
 // (A third form, fp32 scores with a 3-input max and fp32 exp2, packing only the probabilities,
 // issues fewer instructions but needs all 128 scores live in fp32: it spilled and measured
 // 66.8 ms against 62.6 ms for form 1 on 61 482 tokens of 10 247-token prompts.)
-// 320 threads x 200 registers fill the register file (a launch bound of 320 threads would be rounded
-// up to 384 by the compiler and cap the kernel at 168 registers, which spills).
+// 10 warps x 192 registers (6144 per warp, the allocation unit is 512) fill the register file; a
+// launch bound of 320 threads would be rounded up to 384 by the compiler and cap the kernel at 168
+// registers, which spills, and 200 registers round up to 6656 per warp, which does not fit.
 template <int SOFTMAX, int POLY>
-__global__ void __maxnreg__(200)
+__global__ void __maxnreg__(192)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, AttnPrefillArgs a, uint32_t idesc_qk,
                     uint32_t idesc_pv) {

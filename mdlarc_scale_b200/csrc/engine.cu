@@ -552,7 +552,7 @@ static int record_decode_step(arcb_session* s, cudaStream_t stream) {
   CKL(arcb_launch_decode_begin(s->st, ea, stream), "decode_begin");
   for (int l = 0; l < c.n_layers; ++l) {
     int r = run_layer(s, l, B, s->st.pos, s->st.slot, nullptr, s->st.kv_len,
-                      s->desc.stop_on_end ? s->st.finished : nullptr, false, nullptr, stream);
+                      s->desc.stop_on_end == 1 ? s->st.finished : nullptr, false, nullptr, stream);
     if (r) return r;
   }
   HeadArgs ha{};

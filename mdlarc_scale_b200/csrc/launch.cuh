@@ -35,5 +35,7 @@ inline cudaError_t arcb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, 
   const bool pdl = arcb_pdl_enabled() && !arcb_pdl_suppressed();
   cfg.attrs = pdl ? attr : nullptr;
   cfg.numAttrs = pdl ? 1 : 0;
-  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+  if (e != cudaSuccess) cudaGetLastError();   // reported through the return value; do not leave it for the next API call
+  return e;
 }

@@ -262,7 +262,7 @@ head_kernel(HeadArgs a, DecodeState st) {
   int tok = best;
   const bool in_range = out_idx >= 0 && out_idx < st.max_new;
   if (st.forced && in_range) tok = st.forced[(size_t)b * st.max_new + out_idx];
-  else if (st.stop_on_end && st.finished[b]) tok = TOK_END;  // frozen row keeps emitting END
+  else if (st.stop_on_end == 1 && st.finished[b]) tok = TOK_END;  // frozen row keeps emitting END (mode 2: keeps decoding)
   if (in_range) {
     st.out_tokens[(size_t)b * st.max_new + out_idx] = tok;
     if (st.step_logits) {

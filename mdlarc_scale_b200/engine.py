@@ -251,7 +251,7 @@ class Session:
         desc = _lib.SessionDesc(
             n_seqs=self.n_seqs, t_max=self.t_max, max_new=self.max_new,
             max_prefill_tokens=self.max_prefill_tokens, attn_splits=int(attn_splits),
-            stop_on_end=int(bool(stop_on_end)),
+            stop_on_end=(2 if stop_on_end == 2 else int(bool(stop_on_end))),
             d_kv_cache=self.kv_cache.data_ptr(), kv_cache_bytes=kv_bytes,
             d_workspace=self.workspace.data_ptr(), workspace_bytes=ws_bytes,
             d_out_tokens=self.out_tokens.data_ptr(), d_forced=_ptr(self.forced),

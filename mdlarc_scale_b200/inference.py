@@ -9,8 +9,12 @@ Differences from the reference that are part of the design:
   * prompts are packed (no padded positions are computed) and the KV cache is compacted, which
     is exact because attention is permutation-invariant over keys and positions enter only
     through the (x, y, z) RoPE;
-  * a row that has emitted END is frozen and keeps emitting END, whereas the reference keeps
-    sampling from such rows until every row has finished; rows agree through their first END.
+  * by default a row that has emitted END is frozen and keeps emitting END, whereas the reference
+    keeps decoding such rows until every row of its batch has finished (src/inference.py:593-626);
+    rows agree through their first END.  The reference reads a candidate grid after the LAST IO_SEP of
+    the whole row (src/inference.py:906-915), so a finished row that goes on to emit another IO_SEP
+    changes its candidate there and not here.  ``freeze_finished=False`` (``generate_output``,
+    ``predict_with_augmentations``) reproduces the reference's behaviour token for token.
 """
 from __future__ import annotations
 
@@ -93,12 +97,15 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
                     max_prefill_tokens: int = DEFAULT_PREFILL_TOKENS, attn_splits: int = 0,
                     session: Session | None = None, pinned: bool = False,
                     constraints: dict | None = None, temperature: float = 0.0, top_k: int | None = None,
-                    sample_seed: int = 0) -> GenerationTrace:
+                    sample_seed: int = 0, freeze_finished: bool = True) -> GenerationTrace:
     """Prefill + greedy decode of a padded batch given as host arrays; returns device tokens.
 
     ``ids`` int [B, S], ``pos`` int [B, S, 3], ``mask`` bool [B, S] (True = real token).  At most
     ``max_new`` tokens are generated per row.  ``forced`` ([B, max_new]) teacher-forces the fed
-    tokens while logits and argmax are still produced for every step.
+    tokens while logits and argmax are still produced for every step.  With ``stop_on_end`` a row
+    that has emitted END is frozen (it emits END from then on and its attention is skipped) unless
+    ``freeze_finished`` is False, in which case it keeps decoding until every row has emitted END,
+    which is what the reference does.
     """
     dev = engine.device
     B, S = ids.shape
@@ -108,7 +115,8 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
     cap = max(cap, int(lens.max()) + 2, B)
     if session is None:
         session = engine.new_session(
-            B, t_max, max_new, cap, stop_on_end=stop_on_end, attn_splits=attn_splits,
+            B, t_max, max_new, cap, stop_on_end=(2 if stop_on_end and not freeze_finished else stop_on_end),
+            attn_splits=attn_splits,
             forced=None if forced is None else torch.from_numpy(np.ascontiguousarray(forced, dtype=np.int32)),
             want_step_logits=want_logits, constraints=constraints, temperature=temperature,
             top_k=top_k or 0, sample_seed=sample_seed)
@@ -157,13 +165,16 @@ def generate_tokens(engine: Engine, ids: np.ndarray, pos: np.ndarray, mask: np.n
 def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
                     example_ids: torch.Tensor | None = None, attention_mask: torch.Tensor | None = None,
                     max_new_tokens: int = 900, temperature: float = 0.0, top_k: int | None = None,
-                    stop_on_end: bool = True, use_compile: bool = False, constraints=None) -> torch.Tensor:
+                    stop_on_end: bool = True, use_compile: bool = False, constraints=None, *,
+                    freeze_finished: bool = True) -> torch.Tensor:
     """Greedy generation with a static KV cache; same contract as ``src/inference.py:487-628``.
 
     ``model`` is a reference ``TinyTransformer`` (its weights are packed once and cached) or an
     ``Engine``.  Returns ``[batch, seq_len + n_generated]`` int64 on ``input_ids.device``.
     ``use_compile`` is accepted and ignored: the decode step always runs as a CUDA graph.
     ``temperature > 0`` samples (optionally from the ``top_k`` largest logits) instead of argmax.
+    ``freeze_finished=False`` keeps decoding rows that have already emitted END until all rows have (the
+    reference's exact behaviour; the default freezes them, which agrees through each row's first END).
     """
     batch, prompt_len = input_ids.shape
     if attention_mask is not None and tuple(attention_mask.shape) != (batch, prompt_len):
@@ -189,7 +200,7 @@ def generate_output(model, input_ids: torch.Tensor, positions_3d: torch.Tensor,
         seed = int(torch.randint(0, 2 ** 62, (1,)).item())
     trace = generate_tokens(engine, ids, pos, mask, ex, max_new, stop_on_end=stop_on_end,
                             constraints=_constraints_dict(constraints, batch), temperature=float(temperature),
-                            top_k=top_k, sample_seed=seed)
+                            top_k=top_k, sample_seed=seed, freeze_finished=freeze_finished)
     gen = trace.tokens.to(device=input_ids.device, dtype=input_ids.dtype)
     return torch.cat([input_ids, gen], dim=1)
 
@@ -352,7 +363,8 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
                                sample_temperature: float = 0.0, sample_top_k: int | None = None,
                                constrain_decoding: bool = False, palette_penalty: float = 2.0,
                                shape_penalty: float = 2.0, batched: bool = True, use_compile: bool = False,
-                               max_batch_size: int = 16, merge_chunks: bool = True):
+                               max_batch_size: int = 16, merge_chunks: bool = True,
+                               freeze_finished: bool = True):
     """Candidates under all augmentations for AAIVR voting (``src/inference.py:697-920``).
 
     Returns ``[(grid | None, dihedral_idx, colour_perm | None), ...]`` in the reference's order.
@@ -360,6 +372,12 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
     batched path does, so each chunk reproduces its semantics (including which hidden state yields
     the first token of a left-padded row); with ``merge_chunks`` the chunks share one session
     (one prefill, one decode loop for all of them) instead of one ``generate_output`` call each.
+
+    A row that has emitted END is frozen here; the reference keeps decoding it until every row of its
+    16-row chunk has finished and reads the grid after the LAST IO_SEP of the row, so a finished row
+    that later emits another IO_SEP yields a different candidate there.  For exactly the reference's
+    candidates pass ``freeze_finished=False`` together with ``merge_chunks=False`` (one call per chunk,
+    each stopping when its own 16 rows have finished).
     """
     device = torch.device(device)
     engine = _resolve_engine(model, device)
@@ -384,7 +402,8 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
             seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if sample_temperature > 0 else 0
             trace = generate_tokens(engine, ids, pos, mask, np.full(n, example_id, dtype=np.int64),
                                     max_output_tokens, stop_on_end=True, constraints=cons,
-                                    temperature=float(sample_temperature), top_k=sample_top_k, sample_seed=seed)
+                                    temperature=float(sample_temperature), top_k=sample_top_k, sample_seed=seed,
+                                    freeze_finished=freeze_finished)
             gen = trace.tokens.cpu().tolist()
             for i, (d_idx, tag) in enumerate(info):
                 out.append((_grid_after_last_sep([int(t) for t in prompts[i]] + gen[i]), d_idx, tag))
@@ -397,7 +416,8 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
             full = generate_output(engine, ids_t, torch.from_numpy(np.asarray(positions[i])[None]).to(device),
                                    torch.tensor([example_id], dtype=torch.long, device=device),
                                    max_new_tokens=max_output_tokens, temperature=sample_temperature,
-                                   top_k=sample_top_k, stop_on_end=True, constraints=cons)
+                                   top_k=sample_top_k, stop_on_end=True, constraints=cons,
+                                   freeze_finished=freeze_finished)
             out.append((_grid_after_last_sep(full[0].cpu().tolist()), d_idx, tag))
         return out
     chunks = [slice(c0, min(c0 + max_batch_size, len(prompts))) for c0 in range(0, len(prompts), max_batch_size)]
@@ -423,7 +443,7 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
         seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if sample_temperature > 0 else 0
         trace = generate_tokens(engine, ids, pos, mask, np.full(n, example_id, dtype=np.int64), max_output_tokens,
                                 stop_on_end=True, constraints=cons, temperature=float(sample_temperature),
-                                top_k=sample_top_k, sample_seed=seed)
+                                top_k=sample_top_k, sample_seed=seed, freeze_finished=freeze_finished)
         gen = trace.tokens.cpu().tolist()
         for i, (d_idx, tag) in enumerate(info):
             # the reference reads the grid after the last IO_SEP of padding + prompt + generated
@@ -439,7 +459,8 @@ def predict_with_augmentations(model, task: dict, test_idx: int, device, example
                                torch.full((ids.shape[0],), example_id, dtype=torch.long, device=device),
                                attention_mask=torch.from_numpy(mask).to(device),
                                max_new_tokens=max_output_tokens, temperature=sample_temperature,
-                               top_k=sample_top_k, stop_on_end=True, constraints=cons)
+                               top_k=sample_top_k, stop_on_end=True, constraints=cons,
+                               freeze_finished=freeze_finished)
         rows = full.cpu().tolist()
         for i, toks in enumerate(rows):
             d_idx, tag = info[c.start + i]

@@ -518,3 +518,35 @@ def test_argument_and_state_errors():
     with pytest.raises(NotImplementedError):
         Engine(sd, dict(vars(cfg), rope_type="1d"), "cuda:0")
     eng.close()
+
+
+@pytest.mark.parametrize("pad", ["right", "left"])
+def test_unfrozen_rows_reproduce_reference_tokens_after_end(engines, golden_model, pad):
+    """freeze_finished=False: rows that have emitted END keep decoding until every row has, as the
+    reference does (src/inference.py:593-626), so whole rows -- including what early finishers emit
+    after their END -- equal the reference's own generate_output tokens under the margin rule.  The
+    default (frozen rows) agrees through each row's first END and emits END afterwards."""
+    from mdlarc_scale_b200.inference import generate_output
+    eng, cfg, sd = engines["varied", "tc-flash"]
+    k = f"varied_{pad}"
+    ids, pos = torch.from_numpy(golden_model[k + "_ids"]), torch.from_numpy(golden_model[k + "_pos"])
+    ex, mask = torch.from_numpy(golden_model[k + "_ex"]), torch.from_numpy(golden_model[k + "_mask"])
+    S = ids.shape[1]
+    want = golden_model[k + "_gen"]                      # the reference's own output, END stopping on
+    ref = om.generate(sd, cfg, ids, pos, ex, mask, max_new_tokens=48, stop_on_end=True, keep_logits=True)
+    assert np.array_equal(ref.tokens.numpy(), want)      # the oracle continues past END like the reference
+    got = generate_output(eng, ids, pos, ex, mask, max_new_tokens=48, stop_on_end=True, freeze_finished=False)
+    assert got.shape[1] == want.shape[1]
+    after_end = 0
+    for b in range(ids.shape[0]):
+        g, w = got[b, S:].tolist(), want[b, S:].tolist()
+        ok, where = tokens_agree(g, w, [lg[b].numpy() for lg in ref.logits], TOL)
+        assert ok, f"row {b} diverges at generated index {where} with a clear reference margin"
+        if 13 in w:
+            after_end += len(w) - 1 - w.index(13)
+    assert after_end > 0, "no row finished early: the case does not exercise post-END decoding"
+    frozen = generate_output(eng, ids, pos, ex, mask, max_new_tokens=48, stop_on_end=True)
+    for b in range(ids.shape[0]):
+        g = frozen[b, S:].tolist()
+        if 13 in g:
+            assert all(t == 13 for t in g[g.index(13):])
