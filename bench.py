@@ -352,6 +352,34 @@ def profile_long_context(args):
                       "decode_step_gbs_counting_kv_only": attn_bytes / t_decode / 1e9}))
 
 
+def profile_decode_small(args):
+    """The decode step's kernels at the benchmark's batch (M = `--profile-decode-small` sequences, large
+    model) on a deliberately small KV cache: 1 train pair of grids up to 3x3 (prompts of a few dozen
+    tokens), 64 cache positions, 16 decode steps.  A few GB resident, so that multi-pass ncu captures
+    of the length-independent kernels (residual GEMM, RMSNorm, head, decode_begin) stay short."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.engine import Engine
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    dev = torch.device("cuda", 0)
+    cfg, sd = model_state()
+    engine = Engine(sd, cfg, dev)
+    n = args.profile_decode_small
+    tasks = synthetic.capped_tasks(5, n, 1, 1, 1, 3, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    ms = []
+    for _ in range(args.warmup + args.steps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        tr = generate_tokens(engine, ids, pos, mask, None, 16, stop_on_end=False)
+        e1.record()
+        e1.synchronize()
+        ms.append(e0.elapsed_time(e1))
+        del tr
+    print(json.dumps({"profile": "decode step, small cache", "sequences": n, "max_prompt": int(mask.sum(axis=1).max()),
+                      "decode_steps": 15, "ms_per_call": ms}))
+
+
 def profile_fanout(args):
     """The fan-out kernels at the size of the voting configuration (400 synthetic tasks x 8 dihedral
     x 20 colour permutations = 64 000 variants), each as ONE launch through the C ABI with its
@@ -744,6 +772,8 @@ def main():
                     help="only time the fan-out kernels for TASKS synthetic tasks x 8 x 20 variants")
     ap.add_argument("--profile-long", type=int, default=0, metavar="SEQS",
                     help="only run one wave of SEQS 10 247-token prompts + --max-new tokens (long-context decode)")
+    ap.add_argument("--profile-decode-small", type=int, default=0, metavar="SEQS",
+                    help="only run prefill + 15 decode steps of SEQS tiny prompts on a 64-position cache (ncu target)")
     ap.add_argument("--max-new", type=int, default=MAX_NEW,
                     help="tokens generated per sequence (the workload uses 931; smaller only for profiling)")
     args = ap.parse_args()
@@ -773,6 +803,9 @@ def main():
         return
     if args.profile_fanout > 0:
         profile_fanout(args)
+        return
+    if args.profile_decode_small > 0:
+        profile_decode_small(args)
         return
     run_ours(args, rank, world, local_rank)
 

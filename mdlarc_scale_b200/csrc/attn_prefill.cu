@@ -1,8 +1,13 @@
 // Flash-style causal prefill attention on tcgen05 tensor cores with TMEM accumulators.
 //
 // One CTA = up to 256 consecutive query rows of one sequence (two 128-row Q tiles, A and B) x one
-// head.  Warp roles (320 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 softmax
-// group of tile A, warps 6-9 softmax group of tile B (one thread per query row).  Per 128-key tile j:
+// head.  Warp roles (352 threads): warp 0 TMA producer, warp 1 MMA issuer of tile A, warp 2 MMA
+// issuer of tile B, warps 3-6 softmax group of tile A, warps 7-10 softmax group of tile B (one
+// thread per query row; a warp reads the TMEM lane quarter warp % 4).  Each issuer walks its own
+// tile's fixed sequence S(0), S(1), PV(0), S(2), PV(1), ... and BLOCKS on the one barrier its next
+// step needs, so a product is issued the moment its operands are ready (an earlier single issuer
+// polled both tiles' barriers in turn, and a failed mbarrier.try_wait may suspend its thread, which
+// left the tensor pipe idle between steps).  Per 128-key tile j:
 //   TMA        K and V tiles [128 keys][64 dims], 128-byte swizzle, 3-stage ring shared by A and B
 //   MMA        S_x = Q_x K^T   (UMMA 128x128x16 x4, fp32 in TMEM)            x in {A, B}
 //   softmax_x  the row's 128 scores are read once from TMEM into registers; row max;
@@ -46,7 +51,8 @@ constexpr int SMEM_BYTES = 2 * Q_BYTES + KV_STAGES * 2 * KV_TILE_BYTES + 1024 + 
 constexpr int TMEM_COLS = 512;
 constexpr int TMEM_P = 384;
 constexpr float LOG2E = 1.4426950408889634f;
-constexpr int N_THREADS = 320;
+constexpr int N_THREADS = 352;
+constexpr int SOFTMAX_WARP0 = 3;   // first softmax warp
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 #ifndef ARCB_FLASH_POLY_DEFAULT
 #define ARCB_FLASH_POLY_DEFAULT 2
@@ -149,11 +155,10 @@ struct Bars {
 // (A third form, fp32 scores with a 3-input max and fp32 exp2, packing only the probabilities,
 // issues fewer instructions but needs all 128 scores live in fp32: it spilled and measured
 // 66.8 ms against 62.6 ms for form 1 on 61 482 tokens of 10 247-token prompts.)
-// 10 warps x 192 registers (6144 per warp, the allocation unit is 512) fill the register file; a
-// launch bound of 320 threads would be rounded up to 384 by the compiler and cap the kernel at 168
-// registers, which spills, and 200 registers round up to 6656 per warp, which does not fit.
+// 11 warps are allocated as 12 (registers are handed out per group of four warps): 168 registers per
+// thread is what fits, which is also what the launch bound makes the compiler assume.
 template <int SOFTMAX, int POLY>
-__global__ void __maxnreg__(192)
+__global__ void __launch_bounds__(N_THREADS, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, AttnPrefillArgs a, uint32_t idesc_qk,
                     uint32_t idesc_pv) {
@@ -189,22 +194,22 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const int kv0 = a.qblock_kv0[blk];
 
   // visible-key count of this thread's query row and the maxima of the two Q tiles
-  const int grp = (warp >= 6) ? 1 : 0;                 // softmax group / Q tile of this warp
+  const int grp = (warp >= SOFTMAX_WARP0 + 4) ? 1 : 0;    // softmax group / Q tile of this warp
   const int r = (warp & 3) * 32 + lane;                // row inside the Q tile (softmax warps)
   int my_cnt = 0;
-  if (warp >= 2) {
+  if (warp >= SOFTMAX_WARP0) {
     const int qr = grp * BQ + r;
     if (qr < rows) my_cnt = a.kv_count[row0 + qr];
     int mx = my_cnt;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    if (lane == 0) s_max_cnt[warp - 2] = mx;
+    if (lane == 0) s_max_cnt[warp - SOFTMAX_WARP0] = mx;
   }
   if (threadIdx.x == 0) {
     mbar_init(B.q, 1);
     for (int s = 0; s < KV_STAGES; ++s) {
       mbar_init(B.kv_full + 8 * s, 1);
-      mbar_init(B.kv_empty + 8 * s, 1);
+      mbar_init(B.kv_empty + 8 * s, 2);   // one arrival per issuer
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(B.s[x], 1);
@@ -250,20 +255,28 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         tma_load_2d(dst + KV_TILE_BYTES, &tmap_v, h * HD, kv0 + j * BKV, B.kv_full + 8 * s);
       }
     }
-  } else if (warp == 1) {
+  } else if (warp == 1 || warp == 2) {
+    // ---- MMA issuer of Q tile x = warp - 1 ----
     if (lane == 0 && n_tiles > 0) {
-      bool ok = mbar_wait_bounded(B.q, 0);
-      if (!ok) arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
-      const uint64_t dq[2] = {umma_desc_k_sw128(q_smem), umma_desc_k_sw128(q_smem + Q_BYTES)};
-      const int n_x[2] = {n_a, n_b};
-      auto mma_s = [&](int x, int j) {  // S_x = Q_x K(j)^T
+      const int x = warp - 1;
+      const int n_x = x ? n_b : n_a;
+      bool ok = true;
+      auto wait_or_flag = [&](uint32_t bar, uint32_t parity, int code) {
+        if (ok && !mbar_wait_bounded(bar, parity)) {
+          arcb_set_error(a.err, code);
+          ok = false;
+        }
+      };
+      if (n_x > 0) wait_or_flag(B.q, 0, ARCB_DEV_WAIT_TIMEOUT_TMA);
+      const uint64_t dq = umma_desc_k_sw128(q_smem + x * Q_BYTES);
+      auto mma_s = [&](int j) {  // S_x = Q_x K(j)^T
         const uint64_t dk = umma_desc_k_sw128(kv_smem + (j % KV_STAGES) * 2 * KV_TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16(tmem_base + x * 128, dq[x] + 2 * ks, dk + 2 * ks, idesc_qk, ks ? 1u : 0u);
+          umma_f16(tmem_base + x * 128, dq + 2 * ks, dk + 2 * ks, idesc_qk, ks ? 1u : 0u);
         umma_commit(B.s[x]);
       };
-      auto mma_o = [&](int x, int j) {  // O_x (+)= P_x V(j)
+      auto mma_o = [&](int j) {  // O_x (+)= P_x V(j); then this tile is done with K/V stage j
         const uint64_t dv = umma_desc_mn_sw128(kv_smem + (j % KV_STAGES) * 2 * KV_TILE_BYTES + KV_TILE_BYTES);
         const uint32_t d_o = tmem_base + 256 + x * 64;
 #pragma unroll
@@ -274,41 +287,33 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
                       (j | ks) ? 1u : 0u);
         }
         umma_commit(B.o[x]);
+        umma_commit(B.kv_empty + 8 * (j % KV_STAGES));
       };
-      // Event-driven issue: S_x(j+1) as soon as the softmax threads have copied S_x(j) out of TMEM
-      // (sfree) and K(j+1) has landed; O_x += P_x V(j) as soon as P_x(j) is published.  A K/V stage
-      // is released once both Q tiles have issued their PV product on it.
-      int next_s[2] = {0, 0}, next_o[2] = {0, 0}, released = 0;
-      const long long t0 = clock64();
-      while (ok && (next_o[0] < n_x[0] || next_o[1] < n_x[1])) {
-        bool progress = false;
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const int js = next_s[x];
-          if (js < n_x[x] && mbar_try_wait(B.kv_full + 8 * (js % KV_STAGES), (js / KV_STAGES) & 1) &&
-              (js == 0 || mbar_try_wait(B.sfree[x], (js - 1) & 1))) {
-            tc_fence_after();
-            mma_s(x, js);
-            next_s[x] = js + 1;
-            progress = true;
-          }
-          const int jo = next_o[x];
-          if (jo < n_x[x] && jo < next_s[x] && mbar_try_wait(B.p[x], jo & 1)) {
-            tc_fence_after();
-            mma_o(x, jo);
-            next_o[x] = jo + 1;
-            progress = true;
-          }
+      for (int j = 0; ok && j < n_x; ++j) {
+        wait_or_flag(B.kv_full + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1, ARCB_DEV_WAIT_TIMEOUT_TMA);   // K(j) has landed
+        if (j > 0) wait_or_flag(B.sfree[x], (j - 1) & 1, ARCB_DEV_WAIT_TIMEOUT_ACC);   // S(j-1) copied out of TMEM
+        if (!ok) break;
+        tc_fence_after();
+        mma_s(j);
+        if (j > 0) {
+          wait_or_flag(B.p[x], (j - 1) & 1, ARCB_DEV_WAIT_TIMEOUT_ACC);                // P(j-1) published
+          if (!ok) break;
+          tc_fence_after();
+          mma_o(j - 1);
         }
-        while (released < n_tiles && (released >= n_x[0] || next_o[0] > released) &&
-               (released >= n_x[1] || next_o[1] > released)) {
-          umma_commit(B.kv_empty + 8 * (released % KV_STAGES));
-          ++released;
+      }
+      if (ok && n_x > 0) {
+        wait_or_flag(B.p[x], (n_x - 1) & 1, ARCB_DEV_WAIT_TIMEOUT_ACC);
+        if (ok) {
+          tc_fence_after();
+          mma_o(n_x - 1);
         }
-        if (!progress && clock64() - t0 > (1ll << 33)) {
-          arcb_set_error(a.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
-          ok = false;
-        }
+      }
+      // K/V stages this tile does not use (the other tile sees more keys): give them back as soon as
+      // they have landed, in order, so that each arrival counts for the right use of the stage
+      for (int j = n_x; ok && j < n_tiles; ++j) {
+        wait_or_flag(B.kv_full + 8 * (j % KV_STAGES), (j / KV_STAGES) & 1, ARCB_DEV_WAIT_TIMEOUT_TMA);
+        if (ok) mbar_arrive(B.kv_empty + 8 * (j % KV_STAGES));
       }
     }
   } else {

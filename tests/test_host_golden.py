@@ -170,3 +170,20 @@ def test_vectorised_prompt_builder_equals_loop_version():
     toks, pos = D.encode_example_np(big, big[:3, :5])
     want = D.encode_example(big.tolist(), big[:3, :5].tolist())
     assert toks.tolist() == want and np.array_equal(pos, D.compute_positions_3d(want))
+
+
+def test_seeded_weight_generators_share_one_stream():
+    """The product's seeded random-init weights (benchmark, sharded runs) and the oracle's
+    (parity tests, golden fixtures) come from the same generator stream: tensor for tensor equal."""
+    import torch
+    from mdlarc_scale_b200 import synthetic
+    from oracle import arc_model as om
+    for size, seed, gain in (("tiny", 0, 1.0), ("tiny", 3, 8.0), ("small", 0, 8.0)):
+        cfg_d, mine = synthetic.seeded_weights(size, seed, gain)
+        cfg = om.make_config(size, max_seq_len=cfg_d["max_seq_len"])
+        theirs = om.round_bf16(om.init_state(cfg, seed=seed, embed_gain=gain))
+        assert set(mine) == set(theirs)
+        for k in mine:
+            assert torch.equal(mine[k], theirs[k]), (size, seed, k)
+        for f in ("d_model", "n_heads", "n_layers", "d_ff", "vocab_size", "num_examples", "max_x", "max_y", "max_z"):
+            assert cfg_d[f] == getattr(cfg, f)
