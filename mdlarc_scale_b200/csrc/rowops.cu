@@ -22,9 +22,45 @@ __device__ __forceinline__ float row_sumsq(const float* __restrict__ x, int d, i
 }
 
 // out16 = (x * rsqrt(mean(x^2) + eps)) * w    (src/transformer.py:45-48)
+// Rows of up to 128 * NV floats are held in registers: every load of the row is in flight at once
+// and the row is read from memory once.  The sum of squares is accumulated in the same order as
+// row_sumsq, so both forms give the same bits.
+template <int NV>
+__device__ __forceinline__ void row_norm_store_regs(const float* __restrict__ x, const float* __restrict__ w,
+                                                    uint16_t* __restrict__ out, int d, float eps, int act_f16,
+                                                    int lane) {
+  float4 v[NV];
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane * 4 + k * 128;
+    v[k] = (i < d) ? *reinterpret_cast<const float4*>(x + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k)
+    if (lane * 4 + k * 128 < d) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)d + eps);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = lane * 4 + k * 128;
+    if (i < d) {
+      const float4 g = __ldg(reinterpret_cast<const float4*>(w + i));
+      uint2 pk;
+      pk.x = pack2_act((v[k].x * inv) * g.x, (v[k].y * inv) * g.y, act_f16);
+      pk.y = pack2_act((v[k].z * inv) * g.z, (v[k].w * inv) * g.w, act_f16);
+      *reinterpret_cast<uint2*>(out + i) = pk;
+    }
+  }
+}
+
 __device__ __forceinline__ void row_norm_store(const float* __restrict__ x, const float* __restrict__ w,
                                                uint16_t* __restrict__ out, int d, float eps, int act_f16,
                                                int lane) {
+  if (d <= 128 * 2) return row_norm_store_regs<2>(x, w, out, d, eps, act_f16, lane);
+  if (d <= 128 * 6) return row_norm_store_regs<6>(x, w, out, d, eps, act_f16, lane);
+  if (d <= 128 * 10) return row_norm_store_regs<10>(x, w, out, d, eps, act_f16, lane);
+  if (d <= 128 * 16) return row_norm_store_regs<16>(x, w, out, d, eps, act_f16, lane);
   const float ss = row_sumsq(x, d, lane);
   const float inv = rsqrtf(ss / (float)d + eps);
   for (int i = lane * 4; i < d; i += 128) {

@@ -153,23 +153,39 @@ def _embed(sd, cfg, ids, example_ids):
 
 
 @torch.no_grad()
-def forward(sd: dict, cfg: Config, ids, pos, example_ids=None, mask=None, is_causal=True):
-    """TinyTransformer.forward (src/transformer.py:562-599): logits [B, S, 14] in fp32."""
+def forward(sd: dict, cfg: Config, ids, pos, example_ids=None, mask=None, is_causal=True, operand_dtype=None):
+    """TinyTransformer.forward (src/transformer.py:562-599): logits [B, S, 14] in fp32.
+
+    ``operand_dtype`` (torch.float16 / torch.bfloat16) is an error model, not the reference: every
+    matmul and attention OPERAND that a 16-bit-activation pipeline stores in that format (both
+    normalised streams, q, k, v, the attention output, the SwiGLU activations) is rounded to it and
+    all arithmetic stays fp32.  It shows how far ANY such pipeline can be from the fp32 forward."""
     B, S = ids.shape
     H, hd = cfg.n_heads, cfg.d_model // cfg.n_heads
     tables = rope_tables(cfg)
     x = _embed(sd, cfg, ids, example_ids)
     amask = None if mask is None else _sdpa_mask(mask.bool(), x.dtype)
+
+    def r(t):
+        return t if operand_dtype is None else t.to(operand_dtype).to(torch.float32)
+
     for l in range(cfg.n_layers):
         p = f"blocks.{l}."
-        h = rmsnorm(x, sd[p + "ln1.weight"], cfg.norm_eps)
+        h = r(rmsnorm(x, sd[p + "ln1.weight"], cfg.norm_eps))
         qkv = F.linear(h, sd[p + "attn.qkv_proj.weight"]).reshape(B, S, 3, H, hd)
         q, k, v = qkv.unbind(2)
         q, k = apply_rope(cfg, tables, q, k, pos)
-        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                           attn_mask=amask, is_causal=is_causal)
+        q, k, v = r(q), r(k), r(v)
+        o = r(F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                             attn_mask=amask, is_causal=is_causal))
         x = x + F.linear(o.transpose(1, 2).reshape(B, S, -1), sd[p + "attn.out_proj.weight"])
-        x = x + _ffn(sd, p, rmsnorm(x, sd[p + "ln2.weight"], cfg.norm_eps))
+        h2 = r(rmsnorm(x, sd[p + "ln2.weight"], cfg.norm_eps))
+        if operand_dtype is None:
+            x = x + _ffn(sd, p, h2)
+        else:
+            gate = F.silu(F.linear(h2, sd[p + "ffn.fc_gate.weight"], sd[p + "ffn.fc_gate.bias"]))
+            up = F.linear(h2, sd[p + "ffn.fc_up.weight"], sd[p + "ffn.fc_up.bias"])
+            x = x + F.linear(r(gate * up), sd[p + "ffn.fc_down.weight"], sd[p + "ffn.fc_down.bias"])
     return F.linear(rmsnorm(x, sd["ln_f.weight"], cfg.norm_eps), sd["lm_head.weight"])
 
 

