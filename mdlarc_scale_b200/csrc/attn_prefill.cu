@@ -106,14 +106,12 @@ __device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
   asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
   return d;
 }
-// half2(s0 * c + m, s1 * c + m): one two-wide fp32 fused multiply-add, then one rounding to half
-__device__ __forceinline__ __half2 shift_pack_half2(uint32_t s0, uint32_t s1, uint64_t c2, uint64_t m2) {
+// (t0, t1) = (s0 * c + m, s1 * c + m) with one two-wide fp32 fused multiply-add
+__device__ __forceinline__ void shift2_f32(uint32_t s0, uint32_t s1, uint64_t c2, uint64_t m2, float& t0, float& t1) {
   uint64_t sp, tp;
   asm("mov.b64 %0, {%1, %2};" : "=l"(sp) : "r"(s0), "r"(s1));
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(tp) : "l"(sp), "l"(c2), "l"(m2));
-  float t0, t1;
   asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(tp));
-  return __floats2half2_rn(t0, t1);
 }
 
 // 2^t for two packed halves, t <= 8, WITHOUT the special-function unit (9 FMA/ALU-pipe instructions
@@ -391,22 +389,29 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         l *= alpha;
         const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
         const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-m_safe, -m_safe);
-        __half2 h2[64];
+        // Probabilities of 16 keys at a time, kept as eight registers per group so that each group
+        // leaves through one 8-column tensor-memory store without register shuffling.  A pair goes
+        // either to the special-function unit (fp32 exp2 of each shifted score, then one rounding of
+        // the pair to half) or to the FMA pipe (the pair is rounded to half first and the packed
+        // polynomial evaluates both at once).
+        uint32_t pr[8][8];
         float lsum = 0.f;
 #pragma unroll
-        for (int g = 0; g < 8; ++g) {  // 8 half2 = 16 keys = two 16-byte chunks of the P row
+        for (int g = 0; g < 8; ++g) {
           __half2 p[8];
 #pragma unroll
           for (int e = 0; e < 8; ++e) {
-            const int k = g * 8 + e;                    // keys 2k, 2k + 1
-            const __half2 t = shift_pack_half2(sv[k >> 4][(2 * k) & 31], sv[k >> 4][((2 * k) & 31) + 1], sc2, nm2);
-            p[e] = ex2_on_fma<POLY>(e) ? ex2_poly_half2(t) : ex2_half2(t);
+            const int k = g * 8 + e;                    // keys 2k, 2k + 1 = P column k
+            float t0, t1;
+            shift2_f32(sv[k >> 4][(2 * k) & 31], sv[k >> 4][((2 * k) & 31) + 1], sc2, nm2, t0, t1);
+            p[e] = ex2_on_fma<POLY>(e) ? ex2_poly_half2(__floats2half2_rn(t0, t1))
+                                       : __floats2half2_rn(ex2_fast(t0), ex2_fast(t1));
           }
           const __half2 t = __hadd2(__hadd2(__hadd2(p[0], p[1]), __hadd2(p[2], p[3])),
                                     __hadd2(__hadd2(p[4], p[5]), __hadd2(p[6], p[7])));
           lsum += __low2float(t) + __high2float(t);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) h2[g * 8 + e] = p[e];   // keys 16 g .. 16 g + 15 = P columns 8 g .. 8 g + 7
+          for (int e = 0; e < 8; ++e) pr[g][e] = h2_bits(p[e]);
         }
         l += lsum;
         if (j > 0) {
@@ -420,12 +425,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         }
         if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) rescale_o(alpha);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t pk[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) pk[i] = h2_bits(h2[c * 32 + i]);
-          tmem_st_32x32(t_p + c * 32, pk);
-        }
+        for (int g = 0; g < 8; ++g) tmem_st_32x8(t_p + g * 8, pr[g]);
       } else {
         // the row's 128 scores, read once
         uint32_t sv[4][32];
