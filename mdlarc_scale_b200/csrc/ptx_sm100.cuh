@@ -38,12 +38,27 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds and
+// is woken as soon as the phase completes, so a waiting warp takes no issue slots from the others.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.b32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after ~2^31 clock ticks (about a second) and returns false,
 // so a pipeline that lost a transaction cannot hang the GPU.
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
-  while (!mbar_try_wait(bar, parity)) {
+  while (!mbar_try_wait_sleep(bar, parity, 100000u)) {
     if (clock64() - t0 > (1ll << 31)) return false;
   }
   return true;
