@@ -55,7 +55,7 @@ constexpr int N_THREADS = 352;
 constexpr int SOFTMAX_WARP0 = 3;   // first softmax warp
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 #ifndef ARCB_FLASH_SPLIT_DEFAULT
-#define ARCB_FLASH_SPLIT_DEFAULT 0
+#define ARCB_FLASH_SPLIT_DEFAULT 1
 #endif
 #ifndef ARCB_FLASH_POLY_DEFAULT
 #define ARCB_FLASH_POLY_DEFAULT 3
