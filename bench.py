@@ -541,6 +541,14 @@ def vote_pipeline_sample(rank, world, dev, dist, n_tasks: int = 8, perms: int = 
     tasks = synthetic.capped_tasks(2, n_tasks, 2, 4, 1, 30, 2048)
     table = fanout.TaskTable(tasks, dev, num_color_perms=perms)
     vt = table.variants()
+    if dist is not None:
+        # one untimed collective of the same shape first: the first all-gather of a new size pays NCCL's
+        # channel set-up (tens of ms), which is not the cost of the pipeline's collective
+        per = sharding.rows_per_rank(len(vt), world)
+        warm = torch.zeros((world * per, fanout.RECORD_BYTES), dtype=torch.uint8, device=dev)
+        for _ in range(2):
+            dist.all_gather_into_tensor(warm, warm[rank * per: (rank + 1) * per])
+        del warm
     torch.cuda.synchronize(dev)
     if dist is not None:
         dist.barrier()

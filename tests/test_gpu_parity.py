@@ -550,3 +550,26 @@ def test_unfrozen_rows_reproduce_reference_tokens_after_end(engines, golden_mode
         g = frozen[b, S:].tolist()
         if 13 in g:
             assert all(t == 13 for t in g[g.index(13):])
+
+
+def test_sessions_on_a_side_stream_reuse_recycled_workspaces(engines):
+    """Sessions created, used and closed in a loop under a non-default torch stream: the workspace of
+    each new session is a block the caching allocator has just taken back from the previous one, and
+    the session's state is cleared by its first prefill IN STREAM ORDER, so every iteration gives the
+    tokens of the default-stream run."""
+    from mdlarc_scale_b200 import synthetic
+    from mdlarc_scale_b200.inference import generate_tokens, pad_prompts
+    eng, cfg, sd = engines["varied", "tc-flash"]
+    tasks = synthetic.capped_tasks(91, 12, 1, 2, 2, 7, None)
+    prompts, positions = synthetic.prompts_for(tasks)
+    ids, pos, mask = pad_prompts(prompts, positions, left=False)
+    want = generate_tokens(eng, ids, pos, mask, None, 20, stop_on_end=True).tokens.cpu()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(5):
+            tr = generate_tokens(eng, ids, pos, mask, None, 20, stop_on_end=True)
+            got = tr.tokens.cpu()
+            del tr
+            assert torch.equal(got, want)
+    torch.cuda.current_stream().wait_stream(side)
