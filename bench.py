@@ -574,6 +574,7 @@ def vote_pipeline_sample(rank, world, dev, dist, n_tasks: int = 8, perms: int = 
                         f"prompts <= 2048 tokens, greedy to END or {MAX_NEW_FULL} tokens",
             "n_gpus": world, "variants": int(len(vt)), "generate_and_gather_s": t_gen,
             "all_gather_ms": ag_ms, "all_gather_bytes": int(timing.get("gather_bytes", 0)),
+            "wait_for_slowest_rank_ms": float(timing.get("wait_for_slowest_rank_ms", 0.0)),
             "vote_s": t_vote, "generated_tokens": int(gen.sum()), "generated_tokens_per_s": float(gen.sum()) / t_gen,
             "rank_tokens_max_over_mean": max(per_rank) / (sum(per_rank) / len(per_rank)),
             "tasks_with_votes": sum(1 for v in votes.values() if v), "votes_sha256": digest}

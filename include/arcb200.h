@@ -256,6 +256,16 @@ int arcb_op_gemm(const void* d_a16, const void* d_w16, float* d_y, int32_t M, in
 int arcb_op_gemm_residual(const void* d_a16, const void* d_w16, const float* d_bias, float* d_x, int32_t M,
                           int32_t N, int32_t K, int32_t act_format, int32_t gemm_path, void* stream);
 
+/* The same operation through the split-K kernel the decode step uses when a launch has too few
+ * rows to give every SM a 128 x 128 tile (e.g. 1024 x 1280): pairs of CTAs each accumulate half of K
+ * and combine in a fixed order through d_scratch before the one reduce-add per element, so the
+ * result stays deterministic.  arcb_gemm_splitk_scratch_bytes returns the scratch size, or 0 when
+ * the kernel does not apply to the shape (the call is then rejected).  No counterpart in the
+ * reference: it is an implementation of the same nn.Linear + residual add. */
+int64_t arcb_gemm_splitk_scratch_bytes(int32_t M, int32_t N, int32_t K);
+int arcb_op_gemm_residual_splitk(const void* d_a16, const void* d_w16, const float* d_bias, float* d_x, int32_t M,
+                                 int32_t N, int32_t K, int32_t act_format, void* d_scratch, void* stream);
+
 /* Attention of one query vector per item over a cached K/V prefix:
  * F.scaled_dot_product_attention at src/inference.py:452 (is_causal=False, key mask
  * expressed as a length).  q16/out16: [n_items][H][64]; K, V: [B][H][t_max][64] bf16;

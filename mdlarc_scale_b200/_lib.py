@@ -27,7 +27,7 @@ EXPORTS = [
     "arcb_engine_load_tensor", "arcb_session_workspace_bytes", "arcb_kv_cache_bytes",
     "arcb_session_create", "arcb_session_destroy", "arcb_prefill", "arcb_decode",
     "arcb_session_poll", "arcb_engine_saturation_count", "arcb_session_attention_probe", "arcb_launch_count", "arcb_op_rmsnorm", "arcb_op_gemm",
-    "arcb_op_gemm_residual",
+    "arcb_op_gemm_residual", "arcb_gemm_splitk_scratch_bytes", "arcb_op_gemm_residual_splitk",
     "arcb_attn_scratch_bytes", "arcb_op_decode_attention", "arcb_op_decode_attention_static",
     "arcb_op_head", "arcb_build_prompts", "arcb_canonicalize_candidates",
 ]
@@ -140,6 +140,9 @@ def load() -> C.CDLL:
     lib.arcb_op_rmsnorm.argtypes = [vp, vp, vp, i32, i32, f32, i32, vp]
     lib.arcb_op_gemm.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.arcb_op_gemm_residual.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.arcb_gemm_splitk_scratch_bytes.restype = i64
+    lib.arcb_gemm_splitk_scratch_bytes.argtypes = [i32, i32, i32]
+    lib.arcb_op_gemm_residual_splitk.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, vp, vp]
     lib.arcb_attn_scratch_bytes.restype = i64
     lib.arcb_attn_scratch_bytes.argtypes = [i32, i32, i32]
     lib.arcb_op_decode_attention.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp, i32, vp]

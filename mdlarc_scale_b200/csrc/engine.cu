@@ -108,6 +108,7 @@ struct arcb_session {
   uint16_t* k16 = nullptr;  // K/V of one prefill call in the activation format
   uint16_t* v16 = nullptr;
   float* attn_scratch = nullptr;
+  float* gemm_scratch = nullptr;   // split-K partials of the decode step's residual GEMMs
   int* example_ids = nullptr;
   bool use_examples = false;
   DecodeState st{};
@@ -282,7 +283,7 @@ static int choose_splits(const arcb_engine* e, int n_seqs, int requested) {
 }
 
 struct WsLayout {
-  size_t x, xn, q, attn, h, k16, v16, scratch, ints, total;
+  size_t x, xn, q, attn, h, k16, v16, scratch, gemm_scratch, ints, total;
   size_t n_int;
 };
 
@@ -300,6 +301,8 @@ static WsLayout ws_layout(const arcb_engine* e, int B, int P, int splits) {
   w.v16 = off; off = align_up(off + (size_t)P * d * 2, 1024);
   w.scratch = off;
   off = align_up(off + (splits > 1 ? (size_t)B * e->cfg.n_heads * splits * ATTN_SCRATCH_STRIDE * 4 : 0), 256);
+  w.gemm_scratch = off;
+  off = align_up(off + align_up((size_t)B, 128) * d * 4, 256);
   w.ints = off;
   // cur_len, len0, cur_tok, gx, gy, gin, slot, kv_len, example_ids (9 x B) + pos (3 x B) + finished (B bytes, as B ints) + counters
   w.n_int = (size_t)B * 13 + 64;
@@ -345,6 +348,7 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
   s->k16 = reinterpret_cast<uint16_t*>(base + w.k16);
   s->v16 = reinterpret_cast<uint16_t*>(base + w.v16);
   s->attn_scratch = splits > 1 ? reinterpret_cast<float*>(base + w.scratch) : nullptr;
+  s->gemm_scratch = reinterpret_cast<float*>(base + w.gemm_scratch);
   int* ints = reinterpret_cast<int*>(base + w.ints);
   const int B = dsc->n_seqs;
   DecodeState& st = s->st;
@@ -473,6 +477,7 @@ static int run_layer(arcb_session* s, int l, int rows, const int* pos, const int
   // out_proj + residual
   GemmEpilogue er{};
   er.mode = EPI_RESID; er.M = rows; er.N = d; er.x = s->x; er.bias = nullptr; er.act_f16 = f16; er.err = e->d_err;
+  er.splitk_scratch = prefill ? nullptr : s->gemm_scratch;   // sized for the decode step's rows only
   CKL(arcb_launch_gemm(s->attn16, L.w_out, er, d, f16, use_tc_for(e, rows, d, d), stream), "out_proj gemm");
   plain_edges.off();
   CKL(arcb_launch_rmsnorm(s->x, L.ln2_w, s->xn16, rows, d, c.norm_eps, f16, stream), "ln2");
@@ -699,6 +704,25 @@ extern "C" int arcb_op_gemm_residual(const void* a16, const void* w, const float
   GemmEpilogue ep{};
   ep.mode = EPI_RESID; ep.M = M; ep.N = N; ep.x = x; ep.bias = bias;
   CKL(arcb_launch_gemm(a16, w, ep, K, act_format == ARCB_ACT_F16, tc, (cudaStream_t)stream, variant), "gemm");
+  return ARCB_OK;
+}
+
+extern "C" int64_t arcb_gemm_splitk_scratch_bytes(int32_t M, int32_t N, int32_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || ensure_gemm_init() != 0) return 0;
+  if (!arcb_gemm_splitk_bn(M, N, K)) return 0;
+  return (int64_t)align_up((size_t)M, 128) * N * 4;
+}
+
+extern "C" int arcb_op_gemm_residual_splitk(const void* a16, const void* w, const float* bias, float* x, int32_t M,
+                                            int32_t N, int32_t K, int32_t act_format, void* scratch, void* stream) {
+  if (!a16 || !w || !x || M <= 0) return fail(ARCB_E_ARG, "bad gemm arguments");
+  CKL(ensure_gemm_init(), "gemm init");
+  if (N % 128 || !arcb_gemm_tc_supported(M, N, K)) return fail(ARCB_E_ARG, "gemm needs N % 128 == 0 and K % 64 == 0");
+  if (!scratch || !arcb_gemm_splitk_bn(M, N, K))
+    return fail(ARCB_E_ARG, "the split-K kernel does not apply to this shape (arcb_gemm_splitk_scratch_bytes returned 0) or no scratch was given");
+  GemmEpilogue ep{};
+  ep.mode = EPI_RESID; ep.M = M; ep.N = N; ep.x = x; ep.bias = bias; ep.splitk_scratch = reinterpret_cast<float*>(scratch);
+  CKL(arcb_launch_gemm(a16, w, ep, K, act_format == ARCB_ACT_F16, true, (cudaStream_t)stream, 0), "gemm");
   return ARCB_OK;
 }
 

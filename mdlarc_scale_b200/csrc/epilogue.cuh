@@ -18,6 +18,7 @@ struct GemmEpilogue {
   float* y;      // EPI_STORE_F32: [M][N]
   float* x;      // EPI_RESID: residual stream [M][N], updated in place
   const float* bias;  // EPI_RESID: [N] or null; EPI_SWIGLU: [N] packed like the weight rows
+  float* splitk_scratch;  // EPI_RESID, optional: >= 128 * ceil(M / 128) * N floats; allows the split-K kernel for few-row launches
   void* out16;   // EPI_QKV_ROPE: q16 [M][d]; EPI_SWIGLU: h16 [M][N/2]
   // EPI_QKV_ROPE
   const int* pos;   // [M][3] raw (x, y, z); clamped here like RotaryEmbedding3D.apply_rotary

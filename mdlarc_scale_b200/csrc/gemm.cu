@@ -7,6 +7,8 @@
 //                      warp 0 = TMA producer, warp 1 = MMA issuer, warps 2-9 = epilogue.
 //   gemm_simt_kernel : CUDA-core tile kernel for skinny M (weight streaming) and as
 //                      the cross-check of the tensor-core path.
+#include <cstdlib>
+
 #include "gemm.cuh"
 #include "launch.cuh"
 #include "ptx_sm100.cuh"
@@ -635,6 +637,202 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------
+// Split-K residual GEMM for few-row launches (the decode step's out-proj and down projections:
+// M = sequences in flight, N = d_model).  With 128 x 128 tiles such a launch has fewer tiles than
+// SMs (80 for 1024 x 1280) and each CTA streams the whole K extent alone, so the launch is bound by
+// one CTA's operand-stream latency.  Here a cluster of two CTAs owns one 128 x BN output tile and
+// each CTA accumulates HALF of K in its own tensor memory.  CTA 1 then hands its fp32 partial to CTA 0
+// through a small global scratch (written and read with lanes = rows, so every access is a
+// contiguous 512 bytes per warp), ordered by a cluster barrier; CTA 0 adds it to its own accumulator
+// in a FIXED order (own + partner + bias) and issues the same single bulk reduce-add per element as
+// the other kernels.  Every element of x still receives exactly one addend, so the result is
+// deterministic (it differs from the unsplit kernel only by fp32 re-association of the K sum).
+// BN is chosen so that 2 * tiles <= SM count (160 for d_model 1280: 64 tiles, 128 CTAs).
+// ---------------------------------------------------------------------------
+template <int BN>
+struct SkCfg {
+  static constexpr int STAGES = 5;
+  static constexpr int A_BYTES = TC_BM * TC_BK * 2;
+  static constexpr int B_BYTES = BN * TC_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int TMEM_COLS = 256;
+  static constexpr int CHUNKS = BN / 32;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * EPI_STAGE_GROUP_BYTES + 1024 + 256;
+};
+
+template <int BN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tc_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_x, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
+                      float* __restrict__ scratch) {
+  using Cfg = SkCfg<BN>;
+  pdl_launch_dependents();
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  constexpr int RING_BYTES = Cfg::STAGES * Cfg::STAGE_BYTES;
+  const uint32_t bar_base = base + RING_BYTES + 2 * EPI_STAGE_GROUP_BYTES;
+  const uint32_t bar_acc_full = bar_base + 16 * Cfg::STAGES;
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
+      base_ptr + RING_BYTES + 2 * EPI_STAGE_GROUP_BYTES + 16 * Cfg::STAGES + 32);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int tile = blockIdx.x >> 1;
+  const int m_blk = tile / tiles_n, n_blk = tile - m_blk * tiles_n;
+  const int num_k = K / TC_BK;
+  const int kb_split = (num_k + 1) / 2;
+  const int kb0 = rank ? kb_split : 0, kb1 = rank ? num_k : kb_split;   // this CTA's K blocks
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(bar_base + 8 * s, 1);
+      mbar_init(bar_base + 8 * (Cfg::STAGES + s), 1);
+    }
+    mbar_init(bar_acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int kb = kb0, i = 0; kb < kb1; ++kb, ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (i / Cfg::STAGES) & 1;
+        if (!mbar_wait_bounded(bar_base + 8 * (Cfg::STAGES + s), ph ^ 1)) {
+          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_MMA);
+          *abort_flag = 1;
+          break;
+        }
+        if (*abort_flag) break;
+        const uint32_t full = bar_base + 8 * s;
+        const uint32_t a_dst = base + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(full, Cfg::STAGE_BYTES);
+        tma_load_2d(a_dst, &tmap_a, kb * TC_BK, m_blk * TC_BM, full);
+        tma_load_2d(a_dst + Cfg::A_BYTES, &tmap_b, kb * TC_BK, n_blk * BN, full);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      bool ok = true;
+      for (int kb = kb0, i = 0; kb < kb1; ++kb, ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (i / Cfg::STAGES) & 1;
+        if (!mbar_wait_bounded(bar_base + 8 * s, ph)) {
+          arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_TMA);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = base + s * Cfg::STAGE_BYTES;
+        const uint64_t da = umma_desc_k_sw128(a_addr);
+        const uint64_t db = umma_desc_k_sw128(a_addr + Cfg::A_BYTES);
+#pragma unroll
+        for (int k4 = 0; k4 < TC_BK / 16; ++k4) umma_f16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (i | k4) ? 1u : 0u);
+        umma_commit(bar_base + 8 * (Cfg::STAGES + s));
+      }
+      if (ok) umma_commit(bar_acc_full);
+    }
+  }
+  // ---- epilogue warps 2..9: lane quarter = warp % 4, chunk set by (warp - 2) / 4 ----
+  const int quarter = warp & 3;
+  const int col_half = (warp - 2) >> 2;
+  const int row_in_tile = quarter * 32 + lane;
+  constexpr int C_SPLIT = (Cfg::CHUNKS + 1) / 2;   // chunks [0, C_SPLIT) to half 0, the rest to half 1
+  const int c_begin = col_half ? C_SPLIT : 0, c_end = col_half ? Cfg::CHUNKS : C_SPLIT;
+  // partial tile in the scratch: [tile][chunk][float4 column q][row] -> lanes (rows) are contiguous
+  float4* part = reinterpret_cast<float4*>(scratch) + (size_t)tile * (BN / 4) * TC_BM;
+  bool ok = true;
+  if (warp >= 2) {
+    ok = mbar_wait_bounded(bar_acc_full, 0);
+    if (!ok) arcb_set_error(ep.err, ARCB_DEV_WAIT_TIMEOUT_ACC);
+    tc_fence_after();
+    if (rank == 1 && ok) {
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          part[(size_t)(c * 8 + q) * TC_BM + row_in_tile] =
+              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]), __uint_as_float(r[4 * q + 2]),
+                          __uint_as_float(r[4 * q + 3]));
+      }
+    }
+  }
+  // CTA 1's partial is in global memory before CTA 0 reads it (release / acquire at cluster scope)
+  cluster_sync_all();
+  if (warp >= 2 && rank == 0) {
+    // the four warps of a group share named barriers below, so they must leave together
+    ok = !named_bar_or(1 + col_half, 128, !ok);
+    if (ok) {
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      uint8_t* stage_ptr = base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES;
+      const uint32_t stage_smem = base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES;
+      uint8_t* my_row = stage_ptr + row_in_tile * 128;
+      const int sw = row_in_tile & 7;
+      const bool elected = quarter == 0 && lane == 0;
+      const int m0 = m_blk * TC_BM;
+#pragma unroll 1
+      for (int c = c_begin; c < c_end; ++c) {
+        const int n0 = n_blk * BN + c * 32;
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        float4 pv[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) pv[q] = part[(size_t)(c * 8 + q) * TC_BM + row_in_tile];
+        tmem_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float4 v = make_float4(__uint_as_float(r[4 * q]) + pv[q].x, __uint_as_float(r[4 * q + 1]) + pv[q].y,
+                                 __uint_as_float(r[4 * q + 2]) + pv[q].z, __uint_as_float(r[4 * q + 3]) + pv[q].w);
+          if (ep.bias) {
+            const float4 b = __ldg(reinterpret_cast<const float4*>(ep.bias + n0 + 4 * q));
+            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+          }
+          pv[q] = v;
+        }
+        if (elected) bulk_wait_read_all();        // the previous reduce has read the buffer
+        named_bar_sync(1 + col_half, 128);
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(my_row + ((q ^ sw) << 4)) = pv[q];
+        fence_proxy_async_smem();
+        named_bar_sync(1 + col_half, 128);
+        if (elected && m0 < ep.M) {
+          tma_reduce_add_2d(&tmap_x, stage_smem, n0, m0);
+          bulk_commit_group();
+        }
+      }
+      if (elected) bulk_wait_all();
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+// ---------------------------------------------------------------------------
 // CUDA-core kernel: 32 x 128 x 32 tiles, 256 threads, each thread 2 rows x (4 + 4) columns
 // (columns c..c+3 and c+64..c+67 so that the SwiGLU partner columns meet in one thread).
 // ---------------------------------------------------------------------------
@@ -813,6 +1011,10 @@ int arcb_gemm_init() {
   if ((e = set_tc2_smem_attr<EPI_QKV_ROPE>()) != cudaSuccess) return (int)e;
   if ((e = set_tc2_smem_attr<EPI_RESID>()) != cudaSuccess) return (int)e;
   if ((e = set_tc2_smem_attr<EPI_SWIGLU>()) != cudaSuccess) return (int)e;
+  if ((e = cudaFuncSetAttribute(gemm_tc_splitk_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                SkCfg<128>::SMEM_BYTES)) != cudaSuccess) return (int)e;
+  if ((e = cudaFuncSetAttribute(gemm_tc_splitk_kernel<160>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                SkCfg<160>::SMEM_BYTES)) != cudaSuccess) return (int)e;
   {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148);
@@ -862,6 +1064,35 @@ static cudaError_t launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, cons
 
 int arcb_gemm_max_pairs() { return max_pairs(); }
 
+// Column tile of the split-K residual kernel for an M x N x K launch, or 0 when it does not apply:
+// the launch must leave most SMs without a 128 x 128 tile, K must be long enough to be worth
+// halving, and 2 * tiles must fit in one wave of CTA pairs.
+int arcb_gemm_splitk_bn(int M, int N, int K) {
+  static const bool enabled = [] { const char* e = getenv("ARCB_SPLITK"); return !(e && e[0] == '0'); }();  // A/B switch
+  if (!enabled) return 0;
+  const int sms = num_sms(), mp = max_pairs();
+  if (mp <= 0 || K < 1024 || K % TC_BK != 0) return 0;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM;
+  if (tiles_m * ((N + 127) / 128) * 10 >= sms * 7) return 0;   // the plain kernel already fills the machine
+  int best = 0, best_tiles = 0;
+  const int cand[2] = {160, 128};
+  for (int bn : cand) {
+    if (N % bn) continue;
+    const int tiles = tiles_m * (N / bn);
+    if (tiles <= mp && 2 * tiles <= sms && tiles > best_tiles) { best = bn; best_tiles = tiles; }
+  }
+  return best;
+}
+
+template <int BN>
+static cudaError_t launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const GemmEpilogue& ep,
+                                 int K, int act_f16, cudaStream_t stream) {
+  const int tiles_n = ep.N / BN, tiles_m = (ep.M + TC_BM - 1) / TC_BM;
+  const uint32_t idesc = umma_idesc_f16(TC_BM, BN, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
+  return arcb_launch(gemm_tc_splitk_kernel<BN>, dim3(2 * tiles_n * tiles_m), dim3(TC_THREADS), SkCfg<BN>::SMEM_BYTES,
+                     stream, ta, tb, tx, ep, K, idesc, tiles_n, ep.splitk_scratch);
+}
+
 template <int MODE>
 static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue& ep, int K,
                             int act_f16, bool use_tc, int tc_variant, cudaStream_t stream) {
@@ -880,6 +1111,20 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
     CUtensorMap ta, tb;
     int r = arcb_make_tmap_2d_16b(&ta, a16, (uint64_t)M, (uint64_t)K, TC_BM, TC_BK, act_f16);
     if (r) return 1000 + r;
+    if (MODE == EPI_RESID && ep.splitk_scratch && tc_variant == 0) {
+      const int bn = arcb_gemm_splitk_bn(M, N, K);
+      if (bn) {
+        r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, bn, TC_BK, act_f16);
+        if (r) return 1000 + r;
+        CUtensorMap txr;
+        r = make_tmap_resid_f32(&txr, ep.x, (uint64_t)M, (uint64_t)N);
+        if (r) return 1000 + r;
+        const cudaError_t le = bn == 160 ? launch_splitk<160>(ta, tb, txr, ep, K, act_f16, stream)
+                                         : launch_splitk<128>(ta, tb, txr, ep, K, act_f16, stream);
+        arcb_count_launch(1);
+        return (int)le;
+      }
+    }
     r = arcb_make_tmap_2d_16b(&tb, w16, (uint64_t)N, (uint64_t)K, (wide && !pair) ? 256 : 128, TC_BK, act_f16);
     if (r) return 1000 + r;
     CUtensorMap tx = ta;  // only the residual epilogue reads it

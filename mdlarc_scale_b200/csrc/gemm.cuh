@@ -11,6 +11,7 @@
 int arcb_launch_gemm(const void* a16, const void* w16, const GemmEpilogue& ep, int K, int act_f16,
                      bool use_tc, cudaStream_t stream, int tc_variant = 0);
 int arcb_gemm_max_pairs();
+int arcb_gemm_splitk_bn(int M, int N, int K);
 int arcb_gemm_init();
 bool arcb_gemm_tc_supported(int M, int N, int K);
 int arcb_make_tmap_2d_16b(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols,

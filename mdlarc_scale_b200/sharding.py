@@ -226,6 +226,13 @@ def gather_records(rec: torch.Tensor, rank: int, world: int, lengths, group=None
         import torch.distributed as dist
         timed = timing is not None and rec.is_cuda
         if timed:
+            # measurement only: line the ranks up first, so that the events bracket the collective
+            # itself and not the wait for the slowest rank's generation
+            torch.cuda.synchronize(rec.device)
+            t_wait = __import__("time").perf_counter()
+            dist.barrier(group=group)
+            torch.cuda.synchronize(rec.device)
+            timing["wait_for_slowest_rank_ms"] = (__import__("time").perf_counter() - t_wait) * 1e3
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
         dist.all_gather_into_tensor(rec, rec[rank * per: (rank + 1) * per], group=group)

@@ -74,6 +74,38 @@ def test_gemm_residual(lib, path, with_bias, M, N, K):
     assert err < 2e-4 * math.sqrt(K / 64) + 1e-5, f"max abs err {err}"
 
 
+@pytest.mark.parametrize("with_bias", [False, True])
+@pytest.mark.parametrize("M,N,K", [(1024, 1280, 1280), (1024, 1280, 3392), (1000, 1280, 3392), (600, 1024, 1024),
+                                   (1024, 1024, 2752), (333, 1280, 1280)])
+def test_gemm_residual_split_k(lib, with_bias, M, N, K):
+    """The decode step's few-row residual GEMMs through the split-K kernel (pairs of CTAs, half of K
+    each, fixed-order combine through a scratch, one reduce-add per element): against fp64, rows beyond
+    M untouched, bitwise identical when repeated (also with a scratch full of garbage)."""
+    nbytes = lib.arcb_gemm_splitk_scratch_bytes(M, N, K)
+    assert nbytes == ((M + 127) // 128) * 128 * N * 4, "these shapes are the ones the kernel is meant for"
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = to_act(torch.randn(M, K, device="cuda", generator=g), _lib.ACT_F16)
+    w = to_act((torch.randn(N, K, device="cuda", generator=g) / math.sqrt(K)).to(torch.bfloat16).float(), _lib.ACT_F16)
+    bias = torch.randn(N, device="cuda", generator=g) if with_bias else None
+    x0 = torch.randn(M + 3, N, device="cuda", generator=g)
+    outs = []
+    for fill in (0.0, float("nan")):
+        scratch = torch.full((nbytes // 4,), fill, device="cuda")
+        x = x0.clone()
+        _lib.check(lib.arcb_op_gemm_residual_splitk(a.data_ptr(), w.data_ptr(), bias.data_ptr() if with_bias else None,
+                                                    x.data_ptr(), M, N, K, _lib.ACT_F16, scratch.data_ptr(), stream()))
+        torch.cuda.synchronize()
+        outs.append(x)
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(outs[0][M:], x0[M:])
+    ref = x0[:M].double() + a.double() @ w.double().t() + (bias.double() if with_bias else 0.0)
+    err = (outs[0][:M].double() - ref).abs().max().item()
+    assert err < 2e-4 * math.sqrt(K / 64) + 1e-5, f"max abs err {err}"
+    # shapes that already fill the machine, or whose K is short, are refused
+    assert lib.arcb_gemm_splitk_scratch_bytes(20000, 1280, 1280) == 0
+    assert lib.arcb_gemm_splitk_scratch_bytes(1024, 1280, 256) == 0
+
+
 @pytest.mark.parametrize("splits", [1, 4, 7])
 @pytest.mark.parametrize("fmt", [_lib.ACT_F16, _lib.ACT_BF16])
 def test_decode_attention(lib, splits, fmt):
