@@ -465,6 +465,11 @@ def plan_prefill(ids: np.ndarray, pos: np.ndarray, mask: np.ndarray, rows: np.nd
     local = np.searchsorted(rows, seq)  # index of each token's sequence within this call (rows is sorted)
     kv_row = np.where(slot >= 0, kv_base[local] + slot, -1).astype(np.int32)
     qb_kv0 = kv_base[local[qb0]].astype(np.int32) if len(qb0) else np.zeros(0, np.int32)
+    if len(qb0):
+        # most expensive query blocks first (cost = keys visible to the block's last row): the
+        # attention kernel's CTAs are dispatched in this order, so its tail is made of cheap blocks
+        order = np.argsort(-cnt[qb0 + qbn - 1].astype(np.int64), kind="stable")
+        qb0, qbn, qb_kv0 = qb0[order], qbn[order], qb_kv0[order]
     n_kv = int(lens.sum())
     identity = bool(np.array_equal(kv_row[:n_kv], np.arange(n_kv, dtype=np.int32)) and (kv_row[n_kv:] < 0).all())
     return PrefillPlan(

@@ -160,6 +160,10 @@ class TaskTable:
         qb0 = (tok_off[:-1][blk_seq] + 256 * blk_k).astype(np.int32)
         qbn = np.minimum(256, lens[blk_seq] - 256 * blk_k).astype(np.int32)
         qb_kv0 = tok_off[:-1][blk_seq].astype(np.int32)
+        # most expensive blocks first (a block's cost grows with the keys its last row sees), so that
+        # the attention kernel's last CTAs are its cheapest ones
+        order = np.argsort(-(256 * blk_k + qbn), kind="stable")
+        qb0, qbn, qb_kv0 = qb0[order], qbn[order], qb_kv0[order]
         zeros = np.zeros(n, np.int32)
         plan = PrefillPlan(
             n_tokens=total, token_ids=out[0, :total], pos_xyz=out[1:4].reshape(-1)[: 3 * total].view(total, 3),
