@@ -1,6 +1,9 @@
 """Recipe that places the reference project's own hot-path files under ``oracle/_ref/``.
 
-    python oracle/make_ref.py [/path/to/reference]        (default: /root/reference)
+    python oracle/make_ref.py [/path/to/reference]
+
+(default: the ARCB_REFERENCE_ROOT environment variable, else a checkout named ``reference`` next to
+this repository).
 
 Copies, unmodified, ``src/{data,transformer,inference,voting}.py`` and
 ``tests/test_{data,transformer,inference,voting}.py`` from a checkout of the reference project.
@@ -16,12 +19,20 @@ Test infrastructure only: nothing under ``mdlarc_scale_b200/`` reads ``oracle/_r
 """
 from __future__ import annotations
 
+import os
 import shutil
 import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
 DEST = HERE / "_ref"
+
+
+def default_reference_root() -> Path:
+    env = os.environ.get("ARCB_REFERENCE_ROOT")
+    return Path(env) if env else HERE.parent.parent / "reference"
+
+
 SRC_FILES = ["data.py", "transformer.py", "inference.py", "voting.py"]
 TEST_FILES = ["test_data.py", "test_transformer.py", "test_inference.py", "test_voting.py"]
 
@@ -30,9 +41,9 @@ def available() -> bool:
     return all((DEST / "src" / f).exists() for f in SRC_FILES) and all((DEST / "tests" / f).exists() for f in TEST_FILES)
 
 
-def make(reference_root: str | Path = "/root/reference", force: bool = False) -> bool:
+def make(reference_root: str | Path | None = None, force: bool = False) -> bool:
     """Copy the files; returns False (and leaves ``_ref`` as it is) when the checkout is absent."""
-    root = Path(reference_root)
+    root = Path(reference_root) if reference_root is not None else default_reference_root()
     if not (root / "src" / "inference.py").exists():
         return False
     if available() and not force:
@@ -79,6 +90,7 @@ def load_reference_modules(prefix: str = "arcref"):
 
 
 if __name__ == "__main__":
-    ok = make(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv)
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    ok = make(args[0] if args else None, force="--force" in sys.argv)
     print(f"{DEST}: {'ready' if ok else 'reference checkout not found, nothing copied'}")
     sys.exit(0 if ok else 1)
