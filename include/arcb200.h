@@ -36,7 +36,7 @@ extern "C" {
 #define ARCB_ACT_F16 0  /* 16-bit activations held as IEEE half (default)     */
 #define ARCB_ACT_BF16 1 /* 16-bit activations held as bfloat16                */
 
-#define ARCB_GEMM_AUTO 0 /* tcgen05 GEMM when M > 32, weight-streaming below   */
+#define ARCB_GEMM_AUTO 0 /* tcgen05 GEMM wherever the shape allows (K % 64 == 0)   */
 #define ARCB_GEMM_SIMT 1 /* CUDA-core GEMM everywhere (debug cross-check)      */
 #define ARCB_GEMM_TC 2   /* tcgen05 GEMM everywhere                            */
 #define ARCB_GEMM_TC_1CTA 3 /* arcb_op_gemm only: the 1-CTA tcgen05 kernels        */

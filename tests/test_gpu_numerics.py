@@ -35,7 +35,7 @@ def test_rope_epilogue_writes_rotated_keys_and_clamps_positions(gemm_path):
     from mdlarc_scale_b200.engine import Engine, plan_prefill
     cfg, sd = _tiny()
     eng = Engine(sd, cfg, "cuda:0", gemm_path=gemm_path)
-    # 48 rows so that the tensor-core GEMM runs when gemm_path is "auto" (M > 32)
+    # 48 rows: a partial tile of the tensor-core GEMM
     base = [(99, 99, 99), (31, 31, 7), (-1, 0, 9), (0, 0, 7), (5, 7, 3), (30, 29, 1), (0, 0, 0), (17, 2, 4)]
     pos = np.array([base[i % len(base)] for i in range(48)], dtype=np.int64)[None]
     ids = np.full((1, 48), 3, dtype=np.int64)       # one token everywhere: rows differ by position only

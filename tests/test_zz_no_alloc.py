@@ -46,6 +46,11 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         assert torch.isfinite(got.float()).all()
         # same tolerance as the decode-attention kernel test (half outputs)
         assert torch.allclose(got.float(), want.float(), rtol=2 ** -10, atol=2e-3)
+        # and directly against an fp32 softmax attention over each item's visible prefix
+        for b, n in enumerate(lens):
+            att = torch.softmax(torch.einsum("hd,htd->ht", q[b].float(), k[b, :, :n].float()) / 8.0, dim=-1)
+            ref = torch.einsum("ht,htd->hd", att, v[b, :, :n].float())
+            assert torch.allclose(got[b].float(), ref, rtol=2 ** -9, atol=3e-3), b
 
 
 def test_static_scratch_entry_rejects_oversize():
