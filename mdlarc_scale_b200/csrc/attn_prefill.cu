@@ -753,7 +753,10 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
       const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
       const uint64_t sc2 = pack_f32x2(sc, sc), nm2 = pack_f32x2(-m_safe, -m_safe);
       uint32_t pr[4][8];
-      float lsum = 0.f;
+      // the 64 probabilities of this half-tile are summed as packed halves in a balanced tree (they are
+      // at most 2^8 each and almost always at most 1, so the tree stays far inside the half range) and
+      // leave half precision once per tile; the running row sum is fp32
+      __half2 gsum[4];
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         __half2 p[8];
@@ -765,13 +768,13 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
           p[e] = ex2_on_fma<POLY>(e) ? ex2_poly_half2(__floats2half2_rn(t0, t1))
                                      : __floats2half2_rn(ex2_fast(t0), ex2_fast(t1));
         }
-        const __half2 t = __hadd2(__hadd2(__hadd2(p[0], p[1]), __hadd2(p[2], p[3])),
-                                  __hadd2(__hadd2(p[4], p[5]), __hadd2(p[6], p[7])));
-        lsum += __low2float(t) + __high2float(t);
+        gsum[g] = __hadd2(__hadd2(__hadd2(p[0], p[1]), __hadd2(p[2], p[3])),
+                          __hadd2(__hadd2(p[4], p[5]), __hadd2(p[6], p[7])));
 #pragma unroll
         for (int e = 0; e < 8; ++e) pr[g][e] = h2_bits(p[e]);
       }
-      l += lsum;
+      const float2 ts = __half22float2(__hadd2(__hadd2(gsum[0], gsum[1]), __hadd2(gsum[2], gsum[3])));
+      l += ts.x + ts.y;
       if (j > 0) {
         // PV(j-1) must have retired before P is overwritten and O rescaled
         good = mbar_wait_bounded(B.o[grp], (j - 1) & 1);
