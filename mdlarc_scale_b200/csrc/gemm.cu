@@ -149,13 +149,23 @@ __device__ __forceinline__ void epilogue_swiglu_tma(const GemmEpilogue& ep, cons
 // address is per token), and the 16-bit copy -- q16, or the call's K / V scratch when its rows are
 // the packed rows themselves (kv16_identity) -- staged as a 128 x 64 box and written by one bulk
 // tensor store, which also clips the rows beyond the tensor (M, or the scratch's row count).
+//
+// cbox_ptr != nullptr: this warp's 32 rows are consecutive cache rows of one sequence (a prompt run),
+// so the bf16 cache rows of a head are one contiguous 4 KB block: the warp stages them in its own
+// 32 x 64 box (cbox_smem / cbox_ptr, same swizzle) and lane 0 writes the box with one bulk tensor
+// store at cache row cbox_row0 + h * t_max, instead of 32 rows x 4 sixteen-byte stores a row apart.
 __device__ __forceinline__ void epilogue_qkv_tma(const GemmEpilogue& ep, const RopeRow& rr, const CUtensorMap* tmap_q,
                                                  const CUtensorMap* tmap_k, const CUtensorMap* tmap_v, uint32_t t_grp,
                                                  int m0, bool row_ok, int n_grp0, int grp, int row_in_tile,
-                                                 uint32_t stage_smem, uint8_t* stage_ptr, bool elected) {
+                                                 uint32_t stage_smem, uint8_t* stage_ptr, bool elected,
+                                                 const CUtensorMap* tmap_kc = nullptr, const CUtensorMap* tmap_vc = nullptr,
+                                                 uint32_t cbox_smem = 0, uint8_t* cbox_ptr = nullptr,
+                                                 long long cbox_row0 = 0) {
   uint8_t* my_row = stage_ptr + row_in_tile * 128;
   const int sw = row_in_tile & 7;
   const int d = ep.d_model;
+  const int lane = row_in_tile & 31;
+  uint8_t* my_crow = cbox_ptr ? cbox_ptr + lane * 128 : nullptr;
 #pragma unroll 1
   for (int hh = 0; hh < 2; ++hh) {
     const int n_head0 = n_grp0 + hh * 64;
@@ -167,6 +177,11 @@ __device__ __forceinline__ void epilogue_qkv_tma(const GemmEpilogue& ep, const R
     if (staged) {
       if (elected) bulk_wait_read_all();    // the previous store has read the buffer
       named_bar_sync(1 + grp, 128);
+    }
+    const bool cbox = sec > 0 && cbox_ptr != nullptr;   // warp-uniform
+    if (cbox) {
+      if (lane == 0) bulk_wait_read_all();  // this warp's previous cache box has been read
+      __syncwarp();
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -180,7 +195,13 @@ __device__ __forceinline__ void epilogue_qkv_tma(const GemmEpilogue& ep, const R
         if (half == 0) rope_rotate32<0>(ep, rr, v);
         else rope_rotate32<16>(ep, rr, v);
       }
-      if (sec > 0 && row_ok && rr.kv_row >= 0) {
+      if (cbox) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(my_crow + (((half * 4 + q) ^ sw) << 4)) =
+              make_uint4(pack2_bf16(v[8 * q], v[8 * q + 1]), pack2_bf16(v[8 * q + 2], v[8 * q + 3]),
+                         pack2_bf16(v[8 * q + 4], v[8 * q + 5]), pack2_bf16(v[8 * q + 6], v[8 * q + 7]));
+      } else if (sec > 0 && row_ok && rr.kv_row >= 0) {
         __nv_bfloat16* base = (sec == 1) ? ep.kcache : ep.vcache;
         uint4* dst = reinterpret_cast<uint4*>(base + (rr.kv_row + (long long)h * ep.t_max) * ARCB_HEAD_DIM + half * 32);
 #pragma unroll
@@ -201,6 +222,14 @@ __device__ __forceinline__ void epilogue_qkv_tma(const GemmEpilogue& ep, const R
         for (int q = 0; q < 4; ++q)
           dst[q] = make_uint4(pack2_act_chk(v[8 * q], v[8 * q + 1], ep.act_f16, ep.err), pack2_act_chk(v[8 * q + 2], v[8 * q + 3], ep.act_f16, ep.err),
                               pack2_act_chk(v[8 * q + 4], v[8 * q + 5], ep.act_f16, ep.err), pack2_act_chk(v[8 * q + 6], v[8 * q + 7], ep.act_f16, ep.err));
+      }
+    }
+    if (cbox) {
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(sec == 1 ? tmap_kc : tmap_vc, cbox_smem, 0, (int)(cbox_row0 + (long long)h * ep.t_max));
+        bulk_commit_group();
       }
     }
     if (staged) {
@@ -459,23 +488,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 // are signalled in both CTAs by a multicast commit; acc_empty[b] of CTA 0 collects one arrival
 // per epilogue warp of both CTAs.
 // ---------------------------------------------------------------------------
+// The QKV instantiation gives one operand stage to eight 32 x 64 bf16 boxes (one per epilogue warp)
+// through which runs of consecutive cache rows are written as bulk tensor stores.
+template <int MODE>
 struct Tc2Cfg {
   static constexpr int BN = 256;
-  static constexpr int STAGES = 6;
+  static constexpr int STAGES = (MODE == EPI_QKV_ROPE) ? 5 : 6;
   static constexpr int A_BYTES = TC_BM * TC_BK * 2;   // this CTA's 128 rows of A
   static constexpr int B_BYTES = 128 * TC_BK * 2;     // this CTA's 128 rows of W
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int TMEM_COLS = 2 * BN;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+  static constexpr int CBOX_BYTES = (MODE == EPI_QKV_ROPE) ? TC_EPI_WARPS * 32 * 128 : 0;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CBOX_BYTES + 1024 + 256;
 };
 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_y,
-                const __grid_constant__ CUtensorMap tmap_z, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
-                int tiles_total) {
-  using Cfg = Tc2Cfg;
+                const __grid_constant__ CUtensorMap tmap_z, const __grid_constant__ CUtensorMap tmap_kc,
+                const __grid_constant__ CUtensorMap tmap_vc, GemmEpilogue ep, int K, uint32_t idesc, int tiles_n,
+                int tiles_total, int cache_boxes) {
+  using Cfg = Tc2Cfg<MODE>;
   constexpr int BN = Cfg::BN;
   pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
@@ -484,11 +518,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   uint8_t* base_ptr = smem_raw + (base - raw);
   // operand stages | residual staging (EPI_RESID only) | barriers; the same offsets in both CTAs
   constexpr int RING_BYTES = Cfg::STAGES * Cfg::STAGE_BYTES;
-  const uint32_t bar_base = base + RING_BYTES + epi_stage_bytes<MODE>();
+  constexpr int CBOX_OFF = RING_BYTES + epi_stage_bytes<MODE>();
+  const uint32_t bar_base = base + CBOX_OFF + Cfg::CBOX_BYTES;
   const uint32_t bar_acc_full = bar_base + 16 * Cfg::STAGES;
   const uint32_t bar_acc_empty = bar_acc_full + 16;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(
-      base_ptr + RING_BYTES + epi_stage_bytes<MODE>() + 16 * Cfg::STAGES + 32);
+      base_ptr + CBOX_OFF + Cfg::CBOX_BYTES + 16 * Cfg::STAGES + 32);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -510,6 +545,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     if (epi_staged<256, MODE>()) tma_prefetch_desc(&tmap_x);
+    if (MODE == EPI_QKV_ROPE && cache_boxes) {
+      tma_prefetch_desc(&tmap_kc);
+      tma_prefetch_desc(&tmap_vc);
+    }
   }
   if (warp == 1) {
     tmem_alloc_2cta(smem_u32(const_cast<uint32_t*>(tmem_slot)), Cfg::TMEM_COLS);
@@ -613,10 +652,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         RopeRow rr;
         rr.x = rr.y = rr.z = 0; rr.kv_row = -1; rr.row16 = -1;
         if (row_ok) rr = rope_row_ctx(ep, m);
+        // this warp's 32 rows are one run of consecutive cache rows: write them as boxes
+        const long long row0 = __shfl_sync(0xffffffffu, rr.kv_row, 0);
+        const bool run = cache_boxes && __all_sync(0xffffffffu, row_ok && rr.kv_row >= 0 && rr.kv_row == row0 + lane);
+        const int cbox_off = CBOX_OFF + (warp - 2) * (32 * 128);
         epilogue_qkv_tma(ep, rr, &tmap_x, &tmap_y, &tmap_z, t_row + col_half * 128, m_blk * 256 + (int)rank * 128,
                          row_ok, n_blk * BN + col_half * 128, col_half, row_in_tile,
                          base + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES,
-                         base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0);
+                         base_ptr + RING_BYTES + col_half * EPI_STAGE_GROUP_BYTES, quarter == 0 && lane == 0,
+                         &tmap_kc, &tmap_vc, base + cbox_off, run ? base_ptr + cbox_off : nullptr, row0);
       }
       else
         epilogue_tile<BN, MODE>(ep, t_row, m, row_ok, n_blk * BN, col_half);
@@ -626,6 +670,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (lane == 0) mbar_arrive_cta0(bar_acc_empty + 8 * acc);
     }
     if (epi_staged<256, MODE>() && quarter == 0 && lane == 0) bulk_wait_all();
+    else if (MODE == EPI_QKV_ROPE && lane == 0) bulk_wait_all();   // this warp's cache boxes
   }
   tc_fence_before();
   __syncthreads();
@@ -996,7 +1041,7 @@ static int max_pairs() { return g_max_pairs[current_device_slot()]; }
 template <int MODE>
 static cudaError_t set_tc2_smem_attr() {
   return cudaFuncSetAttribute(gemm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>());
+                              Tc2Cfg<MODE>::SMEM_BYTES + epi_stage_bytes<MODE>());
 }
 
 // Opt in to the large dynamic shared memory of every tcgen05 instantiation (call once, outside
@@ -1019,7 +1064,7 @@ int arcb_gemm_init() {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 148);
     cfg.blockDim = dim3(TC_THREADS);
-    cfg.dynamicSmemBytes = Tc2Cfg::SMEM_BYTES + epi_stage_bytes<EPI_RESID>();
+    cfg.dynamicSmemBytes = Tc2Cfg<EPI_RESID>::SMEM_BYTES + epi_stage_bytes<EPI_RESID>();
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
@@ -1052,14 +1097,16 @@ static cudaError_t launch_tc(const CUtensorMap& ta, const CUtensorMap& tb, const
 
 template <int MODE>
 static cudaError_t launch_tc2(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tx, const CUtensorMap& ty,
-                       const CUtensorMap& tz, const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
+                       const CUtensorMap& tz, const CUtensorMap& tkc, const CUtensorMap& tvc, int cache_boxes,
+                       const GemmEpilogue& ep, int K, int act_f16, cudaStream_t stream) {
   const int tiles_n = (ep.N + 255) / 256, tiles_m = (ep.M + 255) / 256;
   const int tiles = tiles_n * tiles_m;
   const int mp = max_pairs();
   const int pairs = tiles < mp ? tiles : mp;
   const uint32_t idesc = umma_idesc_f16(256, 256, act_f16 ? 0 : 1, act_f16 ? 0 : 1);
   return arcb_launch(gemm_tc2_kernel<MODE>, dim3(2 * pairs), dim3(TC_THREADS),
-                     Tc2Cfg::SMEM_BYTES + epi_stage_bytes<MODE>(), stream, ta, tb, tx, ty, tz, ep, K, idesc, tiles_n, tiles);
+                     Tc2Cfg<MODE>::SMEM_BYTES + epi_stage_bytes<MODE>(), stream, ta, tb, tx, ty, tz, tkc, tvc, ep, K, idesc,
+                     tiles_n, tiles, cache_boxes);
 }
 
 int arcb_gemm_max_pairs() { return max_pairs(); }
@@ -1148,8 +1195,23 @@ static int launch_gemm_mode(const void* a16, const void* w16, const GemmEpilogue
         if (r) return 1000 + r;
       }
     }
+    // K / V cache of this layer as [n_seqs * n_heads * t_max][64] bf16, 32-row boxes: prompt runs are
+    // written through them (only when several rows of a launch can share a sequence)
+    CUtensorMap tkc = ta, tvc = ta;
+    int cache_boxes = 0;
+    if (MODE == EPI_QKV_ROPE && pair && ep.seq != nullptr && ep.kcache && ep.vcache) {
+      static const bool boxes_on = [] { const char* e = getenv("ARCB_CACHE_BOXES"); return !(e && e[0] == '0'); }();  // A/B switch
+      const unsigned long long rows = (unsigned long long)ep.n_seqs * ep.n_heads * ep.t_max;
+      if (boxes_on && rows < (1ull << 31)) {
+        r = arcb_make_tmap_2d_16b(&tkc, ep.kcache, rows, 64, 32, 64, 0);
+        if (r) return 1000 + r;
+        r = arcb_make_tmap_2d_16b(&tvc, ep.vcache, rows, 64, 32, 64, 0);
+        if (r) return 1000 + r;
+        cache_boxes = 1;
+      }
+    }
     cudaError_t le;
-    if (pair) le = launch_tc2<MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
+    if (pair) le = launch_tc2<MODE>(ta, tb, tx, ty, tz, tkc, tvc, cache_boxes, ep, K, act_f16, stream);
     else if (wide) le = launch_tc<256, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
     else le = launch_tc<128, MODE>(ta, tb, tx, ty, tz, ep, K, act_f16, stream);
     arcb_count_launch(1);

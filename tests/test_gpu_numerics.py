@@ -71,6 +71,47 @@ def test_rope_epilogue_writes_rotated_keys_and_clamps_positions(gemm_path):
     eng.close()
 
 
+def test_prompt_runs_reach_the_cache_as_boxes_and_single_rows_alike():
+    """A packed prefill large enough for the CTA-pair GEMM (4 838 rows of the tiny model): warps whose 32
+    rows are one run of consecutive cache rows write 32 x 64 boxes, warps that straddle a sequence
+    boundary or the tail write row by row; every K / V row of layer 0 must be the oracle's."""
+    from mdlarc_scale_b200.engine import Engine, plan_prefill
+    cfg, sd = _tiny()
+    eng = Engine(sd, cfg, "cuda:0")
+    lens = [1900, 37, 1500, 1, 1400]
+    B, S = len(lens), max(lens)
+    rng = np.random.default_rng(5)
+    ids = rng.integers(0, 14, size=(B, S)).astype(np.int64)
+    pos = np.stack([rng.integers(0, 31, size=(B, S)), rng.integers(0, 30, size=(B, S)),
+                    rng.integers(0, 5, size=(B, S))], axis=-1).astype(np.int64)
+    mask = np.arange(S)[None, :] < np.array(lens)[:, None]
+    T = S + 4
+    sess = eng.new_session(B, T, 1, int(sum(lens)) + 2 * B, stop_on_end=False)
+    sess.kv_cache.zero_()
+    sess.prefill(plan_prefill(ids, pos, mask, np.arange(B)).to(torch.device("cuda:0")), None)
+    sess.poll()
+    H, hd, L = cfg.n_heads, 64, cfg.n_layers
+    cache = sess.kv_cache.view(torch.bfloat16).view(L, 2, B, H, T, hd)
+    ids_t, pos_t = torch.from_numpy(ids), torch.from_numpy(pos)
+    h = om.rmsnorm(sd["token_embed.weight"][ids_t], sd["blocks.0.ln1.weight"], cfg.norm_eps)
+    q, k, v = torch.nn.functional.linear(h, sd["blocks.0.attn.qkv_proj.weight"]).reshape(B, S, 3, H, hd).unbind(2)
+    _, k_rot = om.apply_rope(cfg, om.rope_tables(cfg), q, k, pos_t)
+    worst = 0.0
+    for b, n in enumerate(lens):
+        k_gpu = cache[0, 0, b, :, :n].float().cpu()                    # [H, n, 64]
+        v_gpu = cache[0, 1, b, :, :n].float().cpu()
+        k_ref, v_ref = k_rot[b, :n].transpose(0, 1), v[b, :n].transpose(0, 1)
+        scale = max(k_ref.abs().max().item(), v_ref.abs().max().item())
+        e = max((k_gpu - k_ref).abs().max().item(), (v_gpu - v_ref).abs().max().item())
+        worst = max(worst, e / scale)
+        assert e < 0.012 * scale, (b, n, e, scale)
+        # nothing was written beyond the prompt (a box must not spill over the run's end)
+        assert not cache[0, :, b, :, n:].any()
+    print(f"cache rows of a 4838-row packed prefill: worst error / scale {worst:.5f}")
+    sess.close()
+    eng.close()
+
+
 def _forward_errors(sd, cfg, seed=71):
     """(GPU vs fp32 oracle, fp32 arithmetic on half-rounded operands vs fp32 oracle, the same with
     bfloat16 operands): each a (max, mean) pair over all valid logits; plus saturation count, tokens."""
