@@ -736,7 +736,7 @@ def run_ours(args, rank, world, local_rank):
             "clocks": clocks,
             "roofline": {"bound": "hbm", "achieved": attn_gbs, "peak": peak, "unit": "GB/s",
                          "frac": attn_gbs / peak, "traffic": attn_bytes * ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE, "peak_kind": peak_kind,
-                         "kernel": "attn_stream_kernel (decode attention)", "ms_per_launch": attn_ms,
+                         "kernel": "attn_stream_coop_kernel (decode attention)", "ms_per_launch": attn_ms,
                          "algorithmic_bytes_per_launch": attn_bytes,
                          "in_graph_sample": {"what": "layer-0 attention launch of the last timed decode step, "
                                                      "CUDA event nodes inside the step graph",

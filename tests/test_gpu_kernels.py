@@ -133,6 +133,39 @@ def test_decode_attention(lib, splits, fmt):
         assert torch.allclose(out[i].float(), ref, rtol=eps, atol=2e-3), (i, (out[i].float() - ref).abs().max())
 
 
+@pytest.mark.parametrize("splits", [1, 3])
+@pytest.mark.parametrize("fmt", [_lib.ACT_F16, _lib.ACT_BF16])
+def test_decode_attention_many_items(lib, splits, fmt):
+    """Launches with at least 296 (item, head, split) work items run the cooperative kernel (eight
+    warps per work item, merged through shared memory): ragged lengths around the 32-row and 256-row
+    slice boundaries, empty and skipped items, permuted cache rows."""
+    B, H, T = 24, 20, 700
+    g = torch.Generator(device="cuda").manual_seed(10 + splits)
+    q = to_act(torch.randn(B, H, 64, device="cuda", generator=g), fmt)
+    k = torch.randn(B, H, T, 64, device="cuda", generator=g).to(torch.bfloat16)
+    v = torch.randn(B, H, T, 64, device="cuda", generator=g).to(torch.bfloat16)
+    lens_l = [1, 31, 32, 33, 255, 256, 257, 700, 0, 511, 513, 64, 96, 300, 699, 2, 16, 48, 128, 384, 640, 5, 650, 289]
+    lens = torch.tensor(lens_l, dtype=torch.int32, device="cuda")
+    seqs = torch.randperm(B, device="cuda", generator=g).to(torch.int32)
+    skip = torch.zeros(B, dtype=torch.uint8, device="cuda")
+    skip[7] = 1
+    out = torch.full((B, H, 64), float("nan"), device="cuda", dtype=q.dtype)
+    scratch = torch.empty(max(1, lib.arcb_attn_scratch_bytes(B, H, splits)), dtype=torch.uint8, device="cuda")
+    _lib.check(lib.arcb_op_decode_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                            seqs.data_ptr(), lens.data_ptr(), skip.data_ptr(), B, H, T, splits,
+                                            scratch.data_ptr(), fmt, stream()))
+    torch.cuda.synchronize()
+    eps = 2 ** -10 if fmt == _lib.ACT_F16 else 2 ** -7
+    for i in range(B):
+        n, s = lens_l[i], int(seqs[i])
+        if n == 0 or i == 7:
+            assert torch.all(out[i] == 0)
+            continue
+        sc = torch.einsum("hd,htd->ht", q[i].float(), k[s, :, :n].float()) / 8.0
+        ref = torch.einsum("ht,htd->hd", torch.softmax(sc, -1), v[s, :, :n].float())
+        assert torch.allclose(out[i].float(), ref, rtol=eps, atol=2e-3), (i, n, (out[i].float() - ref).abs().max())
+
+
 def test_head_logits_argmax(lib):
     rows, d = 37, 1280
     g = torch.Generator(device="cuda").manual_seed(0)
