@@ -4,8 +4,6 @@
 //   decode_begin  : grid-state position update + embedding + first RMSNorm of a decode step
 //   head          : final RMSNorm -> 14 logits -> argmax (+ greedy-loop bookkeeping)
 //   pack_rows     : fp32 -> bf16-rounded weights in kernel layout
-#include <cstdlib>
-
 #include "rowops.cuh"
 #include "launch.cuh"
 
@@ -93,10 +91,9 @@ rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, uint16_
                int rows, int d, float eps, int act_f16) {
   pdl_launch_dependents();
   pdl_wait();
-  // grid-stride over groups of ROWS_PER_CTA rows: a prefill-sized launch keeps a bounded number of
-  // CTAs resident for its whole length instead of starting and retiring one CTA per four rows
-  for (int row = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5); row < rows; row += gridDim.x * ROWS_PER_CTA)
-    row_norm_store(x + (size_t)row * d, w, out + (size_t)row * d, d, eps, act_f16, threadIdx.x & 31);
+  const int row = blockIdx.x * ROWS_PER_CTA + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  row_norm_store(x + (size_t)row * d, w, out + (size_t)row * d, d, eps, act_f16, threadIdx.x & 31);
 }
 
 __global__ void __launch_bounds__(ROWS_PER_CTA * 32)
@@ -345,10 +342,7 @@ int arcb_launch_rmsnorm(const float* x, const float* w, void* out16, int rows, i
                         int act_f16, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (d % 4) return -1;
-  static const int cap = [] { const char* e = getenv("ARCB_RMSNORM_CTAS"); return e ? atoi(e) : 148 * 16; }();  // A/B switch
-  int blocks = (rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA;
-  if (cap > 0 && blocks > cap) blocks = cap;
-  const cudaError_t e = arcb_launch(rmsnorm_kernel, dim3(blocks), dim3(ROWS_PER_CTA * 32), 0,
+  const cudaError_t e = arcb_launch(rmsnorm_kernel, dim3((rows + ROWS_PER_CTA - 1) / ROWS_PER_CTA), dim3(ROWS_PER_CTA * 32), 0,
                                     stream, x, w, reinterpret_cast<uint16_t*>(out16), rows, d, eps, act_f16);
   arcb_count_launch(1);
   return (int)e;
