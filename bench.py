@@ -35,10 +35,10 @@ MAX_NEW_FULL = 931   # the configurations' budget (MAX_NEW may be lowered for pr
 KV_POSITIONS = 1536
 MODEL_SIZE = "large"
 # DRAM traffic of the decode-attention kernel relative to its algorithmic bytes, measured with one
-# ncu capture of the standalone kernel on 256 sequences x 1000 cached positions (1311.40 MB read +
-# 3.6 MB written per launch for 1310.72 MB algorithmic); traffic grows in proportion to the cached
+# ncu capture of the standalone kernel on 256 sequences x 1000 cached positions (1311.5 MB read +
+# 4.0 MB written per launch for 1310.72 MB algorithmic); traffic grows in proportion to the cached
 # positions, so a full-size launch is scaled by its algorithmic bytes.
-ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0033
+ATTN_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0037
 LINEAR_FLOP_PER_TOKEN = 469.9e6          # large model: 2 x matmul parameters
 
 
@@ -243,30 +243,37 @@ def attention_roofline(engine, session, lens0: np.ndarray, n_layers_sampled: int
 
 
 def profile_attention(args):
-    """Standalone decode-attention launches of known size for an ncu capture: `--batch` sequences,
-    20 heads, every sequence `--profile-attn` cached positions; prints the algorithmic bytes."""
+    """Standalone decode-attention launches of known size (for an ncu capture, or an A/B of the kernel
+    variants through their environment switches): `--batch` sequences, 20 heads, `--profile-attn` cached
+    positions per sequence, or lengths drawn uniformly from T - spread .. T + spread with
+    `--profile-attn-spread`; prints the algorithmic bytes and the CUDA-event time of every launch."""
     from mdlarc_scale_b200 import _lib
     lib = _lib.load()
     B, H, T = args.batch, 20, args.profile_attn
+    spread = max(0, min(args.profile_attn_spread, T - 1))
+    t_max = T + spread
     dev = torch.device("cuda", 0)
     q = torch.randn(B, H, 64, device=dev).to(torch.float16)
-    kv = torch.randn(2, B, H, T, 64, device=dev).to(torch.bfloat16)
+    kv = torch.empty(2, B, H, t_max, 64, device=dev, dtype=torch.bfloat16)
+    kv.view(torch.int16).random_(0, 16128)   # bit patterns of finite non-negative bf16 values below 0.5
     out = torch.empty_like(q)
-    lens = torch.full((B,), T, dtype=torch.int32, device=dev)
+    lens_np = np.random.default_rng(3).integers(T - spread, T + spread + 1, size=B).astype(np.int32)
+    lens = torch.from_numpy(lens_np).to(dev)
     ms = []
-    for _ in range(4):
+    for _ in range(8 if spread or B > 256 else 4):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         _lib.check(lib.arcb_op_decode_attention(q.data_ptr(), kv[0].data_ptr(), kv[1].data_ptr(), out.data_ptr(), None,
-                                                lens.data_ptr(), None, B, H, T, 1, None, _lib.ACT_F16,
+                                                lens.data_ptr(), None, B, H, t_max, 1, None, _lib.ACT_F16,
                                                 torch.cuda.current_stream(dev).cuda_stream))
         e1.record()
         e1.synchronize()
         ms.append(e0.elapsed_time(e1))
-    algo = B * H * T * 64 * 2 * 2
-    print(json.dumps({"profile": "decode attention", "batch": B, "heads": H, "cached_positions": T,
+    algo = int(lens_np.sum()) * H * 64 * 2 * 2
+    warm = sorted(ms[2:])
+    print(json.dumps({"profile": "decode attention", "batch": B, "heads": H, "cached_positions": T, "spread": spread,
                       "algorithmic_bytes_per_launch": algo, "ms_per_launch": ms,
-                      "gbs_last": algo / ms[-1] / 1e6}))
+                      "gbs_last": algo / ms[-1] / 1e6, "gbs_median": algo / warm[len(warm) // 2] / 1e6}))
 
 
 def profile_prefill(args):
@@ -775,6 +782,8 @@ def main():
                     help="skip the prefill-heavy prefill call and the sharded vote pipeline sample")
     ap.add_argument("--profile-attn", type=int, default=0, metavar="T",
                     help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
+    ap.add_argument("--profile-attn-spread", type=int, default=0, metavar="S",
+                    help="with --profile-attn: lengths uniform in T - S .. T + S instead of T everywhere")
     ap.add_argument("--profile-prefill", type=int, default=0, metavar="PAIRS",
                     help="only time the prefill of ~64k tokens of prompts with PAIRS 30x30 train pairs")
     ap.add_argument("--profile-fanout", type=int, default=0, metavar="TASKS",
