@@ -97,7 +97,8 @@ def test_prefill_plan_right_and_left_padding():
         assert plan.kv_slot.tolist() == [0, 1, 2, 3, 4, 0, 1, 2, 3, 4, 5, 6, 7]
         assert plan.kv_count.tolist() == [1, 2, 3, 4, 5, 1, 2, 3, 4, 5, 6, 7, 8]
         assert plan.prompt_len.tolist() == [5, 8]
-        assert plan.qblock_row0.tolist() == [0, 5] and plan.qblock_rows.tolist() == [5, 8]
+        # query blocks are listed most expensive first (the block whose last row sees the most keys)
+        assert plan.qblock_row0.tolist() == [5, 0] and plan.qblock_rows.tolist() == [8, 5]
     # a left-padded row whose index len-1 falls in the padding gets a query-only row
     prompts = [[10, 12], [10, 3, 11, 4, 11, 12, 5, 11]]
     positions = [D.compute_positions_3d(p) for p in prompts]
