@@ -251,7 +251,7 @@ def profile_attention(args):
     lib = _lib.load()
     B, H, T = args.batch, 20, args.profile_attn
     spread = max(0, min(args.profile_attn_spread, T - 1))
-    t_max = T + spread
+    t_max = max(T + spread, args.profile_attn_pitch)   # rows between two (sequence, head) streams of the cache
     dev = torch.device("cuda", 0)
     q = torch.randn(B, H, 64, device=dev).to(torch.float16)
     kv = torch.empty(2, B, H, t_max, 64, device=dev, dtype=torch.bfloat16)
@@ -271,7 +271,7 @@ def profile_attention(args):
         ms.append(e0.elapsed_time(e1))
     algo = int(lens_np.sum()) * H * 64 * 2 * 2
     warm = sorted(ms[2:])
-    print(json.dumps({"profile": "decode attention", "batch": B, "heads": H, "cached_positions": T, "spread": spread,
+    print(json.dumps({"profile": "decode attention", "batch": B, "heads": H, "cached_positions": T, "spread": spread, "capacity": t_max,
                       "algorithmic_bytes_per_launch": algo, "ms_per_launch": ms,
                       "gbs_last": algo / ms[-1] / 1e6, "gbs_median": algo / warm[len(warm) // 2] / 1e6}))
 
@@ -608,6 +608,7 @@ def run_ours(args, rank, world, local_rank):
     batches = [make_batch(10_000 * rank + i, B) for i in range(n_total)]
     prefill_cap = 65536
     session = engine.new_session(B, KV_POSITIONS, MAX_NEW, prefill_cap, stop_on_end=False)
+    session_pitch = session.t_max   # rows reserved per (sequence, head): the capacity rounded up to 16 mod 32
 
     def upload(batch):
         ids, pos, mask = batch
@@ -733,9 +734,9 @@ def run_ours(args, rank, world, local_rank):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": "cfg4-large-decode", "model": MODEL_SIZE, "sequences_per_gpu_per_step": B,
-                       "new_tokens": MAX_NEW, "kv_positions": KV_POSITIONS, "stop_on_end": False,
+                       "new_tokens": MAX_NEW, "kv_positions": KV_POSITIONS, "kv_row_pitch": session_pitch, "stop_on_end": False,
                        "activations": "f16 operands, bf16 weights + KV cache, f32 accumulate/residual",
-                       "l2": "inputs larger than L2 (KV cache %.1f GB per GPU)" % (B * KV_POSITIONS * engine.kv_bytes_per_position() / 1e9),
+                       "l2": "inputs larger than L2 (KV cache %.1f GB per GPU)" % (B * session_pitch * engine.kv_bytes_per_position() / 1e9),
                        "parallelism": f"dp{world} (independent sequence shards)"},
             "e2e": {"value": gen_tokens / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": h2d // args.steps,
                     "d2h_bytes_per_step": d2h // args.steps},
@@ -784,6 +785,8 @@ def main():
                     help="only run 4 standalone decode-attention launches over T cached positions (ncu target)")
     ap.add_argument("--profile-attn-spread", type=int, default=0, metavar="S",
                     help="with --profile-attn: lengths uniform in T - S .. T + S instead of T everywhere")
+    ap.add_argument("--profile-attn-pitch", type=int, default=0, metavar="ROWS",
+                    help="with --profile-attn: cache capacity (rows per sequence and head) when larger than T + S")
     ap.add_argument("--profile-prefill", type=int, default=0, metavar="PAIRS",
                     help="only time the prefill of ~64k tokens of prompts with PAIRS 30x30 train pairs")
     ap.add_argument("--profile-fanout", type=int, default=0, metavar="TASKS",

@@ -125,7 +125,10 @@ int arcb_engine_saturation_count(arcb_engine* eng, int64_t* count, int32_t reset
  * (src/inference.py:51-96, 104-168, 539-558). */
 typedef struct arcb_session_desc {
   int32_t n_seqs;             /* B: cache rows                                        */
-  int32_t t_max;              /* cache positions per sequence                         */
+  int32_t t_max;              /* cache positions per sequence; also the row pitch of  */
+                              /* the cache: prefer t_max % 32 == 16 (an odd multiple  */
+                              /* of 2 KB between streams; 1536 or 2048 rows put them  */
+                              /* on the same memory channels: -3 % decode bandwidth)  */
   int32_t max_new;            /* generated-token budget per sequence                  */
   int32_t max_prefill_tokens; /* largest packed-token count of one arcb_prefill call  */
   int32_t attn_splits;        /* split-K factor of decode attention; 0 = choose       */

@@ -45,7 +45,7 @@ def test_rope_epilogue_writes_rotated_keys_and_clamps_positions(gemm_path):
     sess.prefill(plan_prefill(ids, pos, mask, np.arange(1)).to(torch.device("cuda:0")), None)
     sess.poll()
     H, hd, L = cfg.n_heads, 64, cfg.n_layers
-    cache = sess.kv_cache.view(torch.bfloat16).view(L, 2, 1, H, 64, hd)
+    cache = sess.kv_cache.view(torch.bfloat16).view(L, 2, 1, H, sess.t_max, hd)
     k_gpu = cache[0, 0, 0, :, :48].float().cpu()                       # [H, 48, 64]
     v_gpu = cache[0, 1, 0, :, :48].float().cpu()
     # oracle: the same arithmetic in fp32 with the reference's clamp
@@ -91,7 +91,7 @@ def test_prompt_runs_reach_the_cache_as_boxes_and_single_rows_alike():
     sess.prefill(plan_prefill(ids, pos, mask, np.arange(B)).to(torch.device("cuda:0")), None)
     sess.poll()
     H, hd, L = cfg.n_heads, 64, cfg.n_layers
-    cache = sess.kv_cache.view(torch.bfloat16).view(L, 2, B, H, T, hd)
+    cache = sess.kv_cache.view(torch.bfloat16).view(L, 2, B, H, sess.t_max, hd)
     ids_t, pos_t = torch.from_numpy(ids), torch.from_numpy(pos)
     h = om.rmsnorm(sd["token_embed.weight"][ids_t], sd["blocks.0.ln1.weight"], cfg.norm_eps)
     q, k, v = torch.nn.functional.linear(h, sd["blocks.0.attn.qkv_proj.weight"]).reshape(B, S, 3, H, hd).unbind(2)
