@@ -191,12 +191,12 @@ attn_stream_kernel(AttnStreamArgs a) {
 constexpr int COOP_WARPS = 4;
 constexpr int COOP_ROWS = 32;
 
-template <int COOP_WARPS, int COOP_ROWS, int MIN_CTAS>
-__global__ void __launch_bounds__(COOP_WARPS * 32, MIN_CTAS)
+template <int WARPS, int ROWS, int MIN_CTAS>
+__global__ void __launch_bounds__(WARPS * 32, MIN_CTAS)
 attn_stream_coop_kernel(AttnStreamArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float s_part[COOP_WARPS][ATTN_SCRATCH_STRIDE];
+  __shared__ float s_part[WARPS][ATTN_SCRATCH_STRIDE];
   const int lane = threadIdx.x & 31, wj = threadIdx.x >> 5;
   const long long w = blockIdx.x;                       // grid = n_items * n_heads * n_splits exactly
   const int split = (int)(w % a.n_splits);
@@ -243,8 +243,8 @@ attn_stream_coop_kernel(AttnStreamArgs a) {
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 
-  constexpr int U = COOP_ROWS / 4;
-  for (int r0 = begin + wj * COOP_ROWS; r0 < end; r0 += COOP_ROWS * COOP_WARPS) {
+  constexpr int U = ROWS / 4;
+  for (int r0 = begin + wj * ROWS; r0 < end; r0 += ROWS * WARPS) {
     uint4 kk[U], vv[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -313,11 +313,11 @@ attn_stream_coop_kernel(AttnStreamArgs a) {
   // warp 0: merge the warps' partials in a fixed order; lane d holds dims 2d, 2d + 1
   float mt = -INFINITY;
 #pragma unroll
-  for (int j = 0; j < COOP_WARPS; ++j) mt = fmaxf(mt, s_part[j][64]);
+  for (int j = 0; j < WARPS; ++j) mt = fmaxf(mt, s_part[j][64]);
   const float mt_safe = (mt == -INFINITY) ? 0.f : mt;
   float lt = 0.f, o0 = 0.f, o1 = 0.f;
 #pragma unroll
-  for (int j = 0; j < COOP_WARPS; ++j) {
+  for (int j = 0; j < WARPS; ++j) {
     const float sc = exp2f(s_part[j][64] - mt_safe);
     lt += s_part[j][65] * sc;
     const float2 v = *reinterpret_cast<const float2*>(&s_part[j][2 * lane]);
