@@ -188,3 +188,14 @@ def test_seeded_weight_generators_share_one_stream():
             assert torch.equal(mine[k], theirs[k]), (size, seed, k)
         for f in ("d_model", "n_heads", "n_layers", "d_ff", "vocab_size", "num_examples", "max_x", "max_y", "max_z"):
             assert cfg_d[f] == getattr(cfg, f)
+
+
+def test_cache_row_pitch_is_the_next_value_16_mod_32():
+    """The cache's rows per (sequence, head) are an odd multiple of 16 rows (2 KB): never a multiple of
+    64 KB, which is what measurably slows decode attention's streams down."""
+    from mdlarc_scale_b200.engine import cache_row_pitch
+    for t in list(range(1, 200)) + [1536, 1552, 2048, 2979, 11178]:
+        p = cache_row_pitch(t)
+        assert t <= p < t + 32 and p % 32 == 16 and cache_row_pitch(p) == p
+        assert (p * 128) % 65536 != 0
+    assert cache_row_pitch(1536) == 1552 and cache_row_pitch(2048) == 2064
