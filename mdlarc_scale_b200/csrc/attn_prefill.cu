@@ -58,7 +58,7 @@ constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 #define ARCB_FLASH_SPLIT_DEFAULT 1
 #endif
 #ifndef ARCB_FLASH_POLY_DEFAULT
-#define ARCB_FLASH_POLY_DEFAULT 3
+#define ARCB_FLASH_POLY_DEFAULT 2   // of every 8 exp2 pairs on the FMA pipe; with two threads per query row 2 beats 3 by 1.9 % (loop and cold call)
 #endif
 
 // MN-major operand tile [K rows of 128 bytes][64 elements], 128-byte swizzle: 8-row groups are
