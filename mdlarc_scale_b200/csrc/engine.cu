@@ -272,13 +272,23 @@ static bool engine_complete(const arcb_engine* e) {
 // ---------------------------------------------------------------------------
 // session
 // ---------------------------------------------------------------------------
-static int choose_splits(const arcb_engine* e, int n_seqs, int requested) {
+// Split count of decode attention.  t_max = 0: the upper bound used to size the scratch (one warp per
+// work item); with the session's cache capacity known, fewer splits when the launch qualifies for the
+// kernel that puts four warps on every work item (attn_stream.cu), which also spares small batches
+// the merge launch.
+static int choose_splits(const arcb_engine* e, int n_seqs, int requested, int t_max = 0) {
   if (requested > 0) return requested > 64 ? 64 : requested;
   // aim for ~16 resident warps on each of the 148 SMs
   const long long work = (long long)n_seqs * e->cfg.n_heads;
   long long s = (148LL * 16 + work - 1) / work;
   if (s < 1) s = 1;
   if (s > 32) s = 32;
+  static const bool coop_splits = [] { const char* v = getenv("ARCB_COOP_SPLITS"); return !(v && v[0] == '0'); }();  // A/B switch
+  if (t_max > 0 && coop_splits) {
+    long long s4 = (148LL * 4 + work - 1) / work;
+    if (s4 < 1) s4 = 1;
+    if (s4 < s && work * s4 >= 296 && (long long)t_max >= 128 * s4) return (int)s4;
+  }
   return (int)s;
 }
 
@@ -332,8 +342,8 @@ extern "C" int arcb_session_create(arcb_engine* e, const arcb_session_desc* dsc,
     return fail(ARCB_E_ARG, "kv cache too small");
   if (((uintptr_t)dsc->d_kv_cache & 255) || ((uintptr_t)dsc->d_workspace & 255))
     return fail(ARCB_E_ARG, "buffers must be 256-byte aligned");
-  const int splits = choose_splits(e, dsc->n_seqs, dsc->attn_splits);
-  const WsLayout w = ws_layout(e, dsc->n_seqs, dsc->max_prefill_tokens, splits);
+  const int splits = choose_splits(e, dsc->n_seqs, dsc->attn_splits, dsc->t_max);
+  const WsLayout w = ws_layout(e, dsc->n_seqs, dsc->max_prefill_tokens, choose_splits(e, dsc->n_seqs, dsc->attn_splits));
   if ((size_t)dsc->workspace_bytes < w.total) return fail(ARCB_E_ARG, "workspace too small");
   arcb_session* s = new arcb_session();
   s->eng = e;
